@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 from .pool import Pool, PoolError
-from .spec import FixedState, PagedKV
+from .spec import FixedState, PagedKV, PagedLatent
 
 
 @dataclass
@@ -41,12 +41,12 @@ class CacheLayout:
                 continue
             if need is None:
                 continue
-            if isinstance(need, PagedKV):
+            if isinstance(need, (PagedKV, PagedLatent)):
                 groups, members, kind = pg, pm, "paged"
             elif isinstance(need, FixedState):
                 groups, members, kind = sg, sm, "state"
             else:
-                raise TypeError(f"order[{i}] asks for {need!r}; a cache need is PagedKV, FixedState or None")
+                raise TypeError(f"order[{i}] asks for {need!r}; a cache need is PagedKV, PagedLatent, FixedState or None")
             if need in groups:
                 g = groups.index(need)
             else:

@@ -3,6 +3,8 @@
 `PagedKV`: keys and values that grow by one row per token, stored in pages.
 `window`, when set, means that only the last `window` tokens are ever read, so
 pages that lie wholly before the window may be given back.
+`PagedLatent`: one row per token from which keys and values are both derived (a
+compressed latent); paged and windowed like `PagedKV`, but stored once.
 `FixedState`: a tensor of fixed shape per request, stored in a slot.
 Calls of the running order whose needs are equal share one group: one pool of
 pages (or slots) and one block table per request.
@@ -19,8 +21,27 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
 
+    planes = 2                      # keys and values are stored apart
+
     def bytes_per_token(self, itemsize: int) -> int:
         return 2 * self.num_kv_heads * self.head_dim * itemsize
+
+
+@dataclass(frozen=True)
+class PagedLatent:
+    """A row of `width` numbers per token, read both as the key and as the value of one shared head."""
+    width: int
+    window: Optional[int] = None
+
+    planes = 1                      # one tensor serves as keys and as values
+    num_kv_heads = 1
+
+    @property
+    def head_dim(self) -> int:
+        return self.width
+
+    def bytes_per_token(self, itemsize: int) -> int:
+        return self.width * itemsize
 
 
 @dataclass(frozen=True)

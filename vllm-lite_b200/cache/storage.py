@@ -3,7 +3,8 @@
 A paged group with c entries of the running order is one tensor
 [c, 2, pages, kv_heads, page_size, head_dim] (keys at [:, 0], values at [:, 1]):
 a (kv head, page) tile of page_size x head_dim is contiguous, which is what the
-attention kernels read.  A fixed-state group is [c, slots, *shape].  Pages are
+attention kernels read.  A group of latent rows (`PagedLatent`) has one plane,
+[c, 1, pages, 1, page_size, width], handed out both as keys and as values.  A fixed-state group is [c, slots, *shape].  Pages are
 never cleared when they change hands: attention reads only what the block table
 and the positions name.  State slots are zeroed when they are handed out.
 """
@@ -21,7 +22,7 @@ class CacheStorage:
     def __init__(self, layout: CacheLayout, page_size: int, num_pages, max_requests: int, dtype, device):
         self.layout = layout
         counts = [int(num_pages)] * len(layout.paged_groups) if isinstance(num_pages, int) else list(num_pages)
-        self.paged = [torch.zeros((len(members), 2, n, need.num_kv_heads, page_size, need.head_dim),
+        self.paged = [torch.zeros((len(members), need.planes, n, need.num_kv_heads, page_size, need.head_dim),
                                   dtype=dtype, device=device)
                       for need, members, n in zip(layout.paged_groups, layout.paged_members, counts)]
         self.state = [torch.zeros((len(members), max_requests) + tuple(need.shape),
@@ -34,7 +35,7 @@ class CacheStorage:
                 continue
             kind, g, idx, owns = place
             if kind == "paged":
-                self.call_caches.append(CallCache(group=g, k=self.paged[g][idx, 0], v=self.paged[g][idx, 1], writes=owns))
+                self.call_caches.append(CallCache(group=g, k=self.paged[g][idx, 0], v=self.paged[g][idx, self.paged[g].shape[1] - 1], writes=owns))
             else:
                 self.call_caches.append(CallCache(group=g, state=self.state[g][idx], writes=owns))
 

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and to
 the function that turns a configuration into a `ModelPlan`.
 
-The name is `architectures[0]` of config.json.  When that key is absent the
+The name is `architectures[0]` of config.json (or the string `architecture`).  When that key is absent the
 reference's rule applies: `model_type`, lower-cased, among the names an entry
 claims (crates/model/src/qwen3/arch.rs:40-50; the reference's registry is a map
 name -> factory behind a lock, crates/model/src/arch/registry.rs:98-113)."""
@@ -43,6 +43,8 @@ def resolve_architecture(config_json: dict) -> ArchitectureEntry:
     if not isinstance(config_json, dict):
         raise ConfigError("config.json must hold a JSON object")
     archs = config_json.get("architectures")
+    if not (isinstance(archs, list) and archs) and isinstance(config_json.get("architecture"), str):
+        archs = [config_json["architecture"]]          # some configurations name their one architecture as a string
     if isinstance(archs, list) and archs:
         name = archs[0]
         if name in _REGISTRY:

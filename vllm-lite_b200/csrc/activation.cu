@@ -36,3 +36,69 @@ extern "C" int vl_silu_mul(const void* gu, void* out, int dtype, int T, int I, i
         return VL_ERR_UNSUPPORTED;
     return vl_launch_status();
 }
+
+// Gated activations of other feed-forwards, on the same [T, 2I] layouts:  out = f(gate, up)
+//   VL_ACT_SILU          silu(g) * u
+//   VL_ACT_RELU          max(g, 0) * u
+//   VL_ACT_CAPPED_SWISH  g' = min(g, limit), u' = clamp(u, -limit, limit):  g' * sigmoid(alpha * g') * (u' + shift)
+// alpha, limit and shift are the caller's constants (a limit <= 0 means no limit).
+#define VL_ACT_SILU 0
+#define VL_ACT_RELU 1
+#define VL_ACT_CAPPED_SWISH 2
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int group, int act,
+                                 float alpha, float limit, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const size_t gi = group > 0 ? (size_t)2 * group * (i / group) + i % group : (size_t)i;
+    float g = to_f32(gu[t * 2 * (size_t)I + gi]);
+    float u = to_f32(gu[t * 2 * (size_t)I + gi + (group > 0 ? group : I)]);
+    float r;
+    if (act == VL_ACT_RELU) {
+        r = fmaxf(g, 0.f) * u;
+    } else if (act == VL_ACT_CAPPED_SWISH) {
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        r = g / (1.0f + expf(-alpha * g)) * (u + shift);
+    } else {
+        r = g / (1.0f + expf(-g)) * u;
+    }
+    out[idx] = from_f32<T>(r);
+}
+
+extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, int group, int act, float alpha,
+                            float limit, float shift, void* stream) {
+    if (T <= 0 || I <= 0) return VL_OK;
+    if (group < 0 || (group > 0 && I % group) || act < 0 || act > 2) return VL_ERR_ARGUMENT;
+    const size_t total = (size_t)T * I;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total, group,
+                         act, alpha, limit, shift);
+    if (dtype == VL_BF16)
+        return vl_launch(gated_act_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, total, group,
+                         act, alpha, limit, shift);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// Logits of a scaled, capped output head, in place on float32:  z <- cap * tanh(z * scale / cap)
+// (cap <= 0: only the scale).
+__global__ void scale_softcap_kernel(float* __restrict__ z, size_t n, float scale, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = z[i] * scale;
+    z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+extern "C" int vl_scale_softcap(float* z, long long n, float scale, float cap, void* stream) {
+    if (n <= 0) return VL_OK;
+    const unsigned blocks = (unsigned)(((size_t)n + 255) / 256);
+    return vl_launch(scale_softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, z, (size_t)n, scale, cap);
+}

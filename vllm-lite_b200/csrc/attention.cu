@@ -39,7 +39,7 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ req_index, const int* __restrict__ positions,
                        int nq, int nkv, int page_size, int num_pages, float scale, int window,
-                       unsigned* err) {
+                       const float* __restrict__ sinks, unsigned* err) {
     constexpr int HD = R * 16;
     __shared__ float s_acc[ATT_GROUPS][HD];
     __shared__ float s_m[ATT_GROUPS], s_l[ATT_GROUPS];
@@ -114,6 +114,9 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     float M = -INFINITY;
 #pragma unroll
     for (int i = 0; i < ATT_GROUPS; ++i) M = fmaxf(M, s_m[i]);
+    // a sink: one more term exp(sink_h) in the denominator, with no key, no value and no scale
+    const float sink = sinks ? sinks[h] : -INFINITY;
+    M = fmaxf(M, sink);
     T* op = out + ((size_t)t * nq + h) * HD;
     for (int e = threadIdx.x; e < HD; e += ATT_THREADS) {
         float L = 0.f, o = 0.f;
@@ -123,6 +126,7 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
             L += s_l[i] * wgt;
             o += s_acc[i][e] * wgt;
         }
+        if (sinks) L += expf(sink - M);
         op[e] = from_f32<T>(L > 0.f ? o / L : 0.f);
     }
 }
@@ -131,12 +135,12 @@ template <typename T>
 static int launch_paged_attention(int R, dim3 grid, cudaStream_t s, const T* q, int q_stride, T* out,
                                   const T* kc, const T* vc, const int* bt, int max_blocks,
                                   const int* req, const int* pos, int nq, int nkv, int page_size,
-                                  int num_pages, float scale, int window, unsigned* err) {
+                                  int num_pages, float scale, int window, const float* sinks, unsigned* err) {
 #define ATT_CASE(RR)                                                                              \
     case RR:                                                                                      \
         paged_attention_kernel<T, RR><<<grid, ATT_THREADS, 0, s>>>(                               \
             q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,    \
-            scale, window, err);                                                                  \
+            scale, window, sinks, err);                                                           \
         break;
     switch (R) {
         ATT_CASE(1) ATT_CASE(2) ATT_CASE(3) ATT_CASE(4) ATT_CASE(5) ATT_CASE(6) ATT_CASE(7) ATT_CASE(8)
@@ -152,7 +156,7 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
                                   const int* block_table, int max_blocks,
                                   const int* req_index, const int* positions,
                                   int T, int nq, int nkv, int hd, int page_size, int num_pages,
-                                  float scale, int window, unsigned* err, void* stream) {
+                                  float scale, int window, const float* sinks, unsigned* err, void* stream) {
     if (T <= 0) return VL_OK;
     if (hd <= 0 || hd % 16 || hd > ATT_MAX_HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0) return VL_ERR_ARGUMENT;
@@ -163,12 +167,12 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
         return launch_paged_attention<float>(hd / 16, grid, s, (const float*)q, q_stride, (float*)out,
                                              (const float*)kcache, (const float*)vcache, block_table,
                                              max_blocks, req_index, positions, nq, nkv, page_size,
-                                             num_pages, scale, window, err);
+                                             num_pages, scale, window, sinks, err);
     if (dtype == VL_BF16)
         return launch_paged_attention<bf16>(hd / 16, grid, s, (const bf16*)q, q_stride, (bf16*)out,
                                             (const bf16*)kcache, (const bf16*)vcache, block_table,
                                             max_blocks, req_index, positions, nq, nkv, page_size,
-                                            num_pages, scale, window, err);
+                                            num_pages, scale, window, sinks, err);
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -147,6 +147,78 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, siz
     if (i < n) out[i] = from_f32<TO>(to_f32(in[i]));
 }
 
+// Layer norm with a weight and no bias, h = (y - mean y) / sqrt(var y + eps) * w with the variance as the mean of the
+// squared deviations (two passes over the row, float32), in the two places a block that norms its sub-layers'
+// OUTPUTS needs it:
+//   layernorm_add_kernel   x[r] += LN(y[r]) * w  (y: a sub-layer's output in the activation dtype; x: the float32
+//                          stream) and, when asked, cast[r] = x[r] in the activation dtype: the next sub-layer's input
+//   layernorm_rows_kernel  out[r] = LN(x[rows[r]]) * w  (the model's last norm on the rows whose logits are wanted)
+// One block of 256 threads per row; the order of the sums depends on the row length alone.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+layernorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
+                     TA* __restrict__ cast, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const TA* yr = y + (size_t)r * H;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) s += to_f32(yr[i]);
+    const float mean = block_sum<256>(s, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) { const float d = to_f32(yr[i]) - mean; ss += d * d; }
+    const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
+    float* xr = x + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += 256) {
+        const float v = xr[i] + (to_f32(yr[i]) - mean) * inv * w[i];
+        xr[i] = v;
+        if (cast) cast[(size_t)r * H + i] = from_f32<TA>(v);
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                      float eps, TA* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) s += xr[i];
+    const float mean = block_sum<256>(s, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) { const float d = xr[i] - mean; ss += d * d; }
+    const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += 256) out[(size_t)r * H + i] = from_f32<TA>((xr[i] - mean) * inv * w[i]);
+}
+
+extern "C" int vl_layernorm_add(const void* y, int act_dtype, const float* w, float eps, float* x, void* cast,
+                                int R, int H, void* stream) {
+    if (R <= 0) return VL_OK;
+    if (H <= 0) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == VL_F32)
+        return vl_launch(layernorm_add_kernel<float>, dim3(R), dim3(256), 0, s, (const float*)y, w, eps, x, (float*)cast, H);
+    if (act_dtype == VL_BF16)
+        return vl_launch(layernorm_add_kernel<bf16>, dim3(R), dim3(256), 0, s, (const bf16*)y, w, eps, x, (bf16*)cast, H);
+    return VL_ERR_UNSUPPORTED;
+}
+
+extern "C" int vl_layernorm_rows(const float* x, const int* rows, const float* w, float eps, void* out, int act_dtype,
+                                 int R, int H, void* stream) {
+    if (R <= 0) return VL_OK;
+    if (H <= 0) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == VL_F32)
+        return vl_launch(layernorm_rows_kernel<float>, dim3(R), dim3(256), 0, s, x, rows, w, eps, (float*)out, H);
+    if (act_dtype == VL_BF16)
+        return vl_launch(layernorm_rows_kernel<bf16>, dim3(R), dim3(256), 0, s, x, rows, w, eps, (bf16*)out, H);
+    return VL_ERR_UNSUPPORTED;
+}
+
 extern "C" int vl_embed(const int* ids, const void* table, int table_dtype, float* x,
                         int T, int H, int V, unsigned* err, void* stream) {
     if (T <= 0) return VL_OK;

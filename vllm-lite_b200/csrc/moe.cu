@@ -1,0 +1,212 @@
+// Routed feed-forwards (mixtures of experts): routing, sorting rows by expert, and putting the
+// experts' results back together.  The products themselves are the grouped form of
+// gemm_batched.cu, the experts' activation is in activation.cu.
+//
+//   vl_moe_route    z = W_r h (float32), score = sigmoid(z) or softmax(z); the `top` largest scores
+//                   pick the experts of a token (ties: the lower index), weights = the scores as they
+//                   are or divided by their sum.  -> expert ids [T, top], weights float32 [T, top]
+//   vl_moe_align    sorts the T * top (token, choice) pairs by expert into tiles of `bm` rows, every
+//                   expert's rows padded up to whole tiles: sorted_rows[r] = pair or -1,
+//                   tile_group[y] = expert of tile y or -1, place[pair] = r.  One block; where a pair
+//                   lands among its expert's rows is not fixed from run to run, and nothing depends
+//                   on it: a row's arithmetic does not depend on its place.
+//   vl_moe_gather   rows[r] = weight(pair) * h[token(pair)] (or h itself), zeros for padding rows
+//   vl_moe_combine  out[t] = sum over the token's choices, in the order of the choices, of
+//                   (weight *) result[place[pair]]
+//
+// Padded tokens of a graph step are ordinary rows here: they cost a row of work and nobody reads
+// their result.
+#include "common.cuh"
+
+#define MOE_SCORE_SIGMOID 0
+#define MOE_SCORE_SOFTMAX 1
+#define MOE_MAX_EXPERTS 1024
+
+// one warp per token
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, int ntok, int E, int K, int top,
+                 int score_fn, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float s_scores[];                  // [4][E]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= ntok) return;
+    float* sc = s_scores + (size_t)warp * E;
+    const T* row = h + (size_t)t * K;
+    for (int e = 0; e < E; ++e) {
+        const float* w = wr + (size_t)e * K;
+        float acc = 0.f;
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(row[k]), w[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) sc[e] = acc;
+    }
+    __syncwarp();
+    if (score_fn == MOE_SCORE_SOFTMAX) {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(sc[e] - m);
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - m) / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
+    }
+    __syncwarp();
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            if (v > best) { best = v; arg = e; }         // ascending e within a lane: the lower index wins a tie
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = arg;
+            weights[(size_t)t * top + j] = best;
+            sc[arg] = -INFINITY;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= total;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ ids, int npairs, int E, int bm, int cap, int max_tiles,
+                 int* __restrict__ sorted_rows, int* __restrict__ tile_group, int* __restrict__ place) {
+    __shared__ int s_count[MOE_MAX_EXPERTS];
+    __shared__ int s_start[MOE_MAX_EXPERTS];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += 1024) s_count[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < npairs; p += 1024) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&s_count[e], 1);
+    }
+    for (int r = tid; r < cap; r += 1024) sorted_rows[r] = -1;
+    for (int y = tid; y < max_tiles; y += 1024) tile_group[y] = -1;
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            s_start[e] = at;
+            const int tiles = (s_count[e] + bm - 1) / bm;
+            for (int y = 0; y < tiles; ++y) tile_group[at / bm + y] = e;
+            at += tiles * bm;
+            s_count[e] = 0;                              // now the cursor of the expert's rows
+        }
+    }
+    __syncthreads();
+    for (int p = tid; p < npairs; p += 1024) {
+        const int e = ids[p];
+        if (e < 0 || e >= E) { place[p] = -1; continue; }
+        const int r = s_start[e] + atomicAdd(&s_count[e], 1);
+        sorted_rows[r] = p;
+        place[p] = r;
+    }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ sorted_rows,
+                                  const float* __restrict__ weights, int top, int K, int scale_input,
+                                  T* __restrict__ rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int p = sorted_rows[r];
+    T* dst = rows + (size_t)r * K;
+    if (p < 0) {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_f32<T>(0.f);
+        return;
+    }
+    const T* src = h + (size_t)(p / top) * K;
+    const float w = scale_input ? weights[p] : 1.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = scale_input ? from_f32<T>(w * to_f32(src[k])) : src[k];
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ result, const int* __restrict__ place,
+                                   const float* __restrict__ weights, int top, int N, int scale_output,
+                                   T* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int r = place[(size_t)t * top + j];
+            if (r < 0) continue;
+            const float v = to_f32(result[(size_t)r * N + n]);
+            acc += scale_output ? weights[(size_t)t * top + j] * v : v;
+        }
+        out[(size_t)t * N + n] = from_f32<T>(acc);
+    }
+}
+
+extern "C" int vl_moe_route(const void* h, int dtype, const float* wr, int T, int E, int K, int top,
+                            int score_fn, int renorm, int* ids, float* weights, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || K <= 0) return VL_ERR_ARGUMENT;
+    if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)4 * E * sizeof(float);
+    const dim3 grid((T + 3) / 4);
+    if (dtype == VL_F32)
+        return vl_launch(moe_route_kernel<float>, grid, dim3(128), smem, s, (const float*)h, wr, T, E, K, top, score_fn,
+                         renorm, ids, weights);
+    if (dtype == VL_BF16)
+        return vl_launch(moe_route_kernel<bf16>, grid, dim3(128), smem, s, (const bf16*)h, wr, T, E, K, top, score_fn,
+                         renorm, ids, weights);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)
+// rounded up to bm is always enough); max_tiles = cap / bm.
+extern "C" int vl_moe_align(const int* ids, int npairs, int E, int bm, int cap, int* sorted_rows, int* tile_group,
+                            int* place, void* stream) {
+    if (npairs <= 0) return VL_OK;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || bm <= 0 || cap % bm || cap < npairs) return VL_ERR_ARGUMENT;
+    if ((long long)cap < (long long)npairs + (long long)min(E, npairs) * (bm - 1)) return VL_ERR_ARGUMENT;
+    return vl_launch(moe_align_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, ids, npairs, E, bm, cap, cap / bm,
+                     sorted_rows, tile_group, place);
+}
+
+extern "C" int vl_moe_gather(const void* h, int dtype, const int* sorted_rows, const float* weights, int cap, int top,
+                             int K, int scale_input, void* rows, void* stream) {
+    if (cap <= 0) return VL_OK;
+    if (top <= 0 || K <= 0) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(moe_gather_kernel<float>, dim3(cap), dim3(128), 0, s, (const float*)h, sorted_rows, weights, top, K,
+                         scale_input, (float*)rows);
+    if (dtype == VL_BF16)
+        return vl_launch(moe_gather_kernel<bf16>, dim3(cap), dim3(128), 0, s, (const bf16*)h, sorted_rows, weights, top, K,
+                         scale_input, (bf16*)rows);
+    return VL_ERR_UNSUPPORTED;
+}
+
+extern "C" int vl_moe_combine(const void* result, int dtype, const int* place, const float* weights, int T, int top,
+                              int N, int scale_output, void* out, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (top <= 0 || N <= 0) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(moe_combine_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)result, place, weights, top, N,
+                         scale_output, (float*)out);
+    if (dtype == VL_BF16)
+        return vl_launch(moe_combine_kernel<bf16>, dim3(T), dim3(128), 0, s, (const bf16*)result, place, weights, top, N,
+                         scale_output, (bf16*)out);
+    return VL_ERR_UNSUPPORTED;
+}

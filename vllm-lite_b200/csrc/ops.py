@@ -41,7 +41,7 @@ _SIGNATURES = {
                                               c_void_p, c_void_p],
     ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, c_void_p, c_void_p],
+                                          c_float, c_int, c_void_p, c_void_p, c_void_p],
     ("attention", "vl_decode_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -62,6 +62,18 @@ _SIGNATURES = {
                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("activation", "vl_gated_act"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    ("activation", "vl_scale_softcap"): [c_void_p, c_longlong, c_float, c_float, c_void_p],
+    ("embed_norm", "vl_layernorm_add"): [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("embed_norm", "vl_layernorm_rows"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("latent", "vl_latent_norm_write"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p],
+    ("gemm_batched", "vl_gemm_batched_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("moe", "vl_moe_align"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("moe", "vl_moe_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("moe", "vl_moe_combine"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p, c_int, c_void_p],
@@ -228,9 +240,18 @@ def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, eps, inv_freq,
 
 
 # ---------------------------------------------------------------- attention
+def _check_sinks(sinks, num_heads):
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks", 1)
+        if sinks.shape[0] != num_heads:
+            raise KernelError(f"sinks must hold one number per query head ({num_heads}), got {sinks.shape[0]}")
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, positions,
-                    num_heads, num_kv_heads, head_dim, scale, window, err):
-    """out [T, nq*hd] = attention of the q part of qkv over the pages of each token's request."""
+                    num_heads, num_kv_heads, head_dim, scale, window, err, sinks=None):
+    """out [T, nq*hd] = attention of the q part of qkv over the pages of each token's request.
+    `sinks` (float32 [nq]): one more term exp(sinks[h]) in every softmax denominator of head h."""
+    _check_sinks(sinks, num_heads)
     _need(qkv, None, "qkv", 2); _need(out, qkv.dtype, "out", 2)
     _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
     _need(block_table, torch.int32, "block_table", 2)
@@ -246,7 +267,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, position
         _ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
         _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
         T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), _ptr(err), _stream()), "vl_paged_attention")
+        float(scale), int(window or 0), _ptr(sinks), _ptr(err), _stream()), "vl_paged_attention")
     return out
 
 
@@ -498,6 +519,167 @@ def silu_mul(gate_up, out, group=0):
         raise KernelError("silu_mul: out must be [T, I] for gate_up [T, 2I]")
     _check(_fn("activation", "vl_silu_mul")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, int(group),
                                             _stream()), "vl_silu_mul")
+    return out
+
+
+ACTIVATIONS = {"silu": 0, "relu": 1, "capped_swish": 2}
+
+
+def gated_act(gate_up, out, act, group=0, alpha=1.0, limit=0.0, shift=0.0):
+    """out[t, i] = f(gate_i, up_i) of gate_up [T, 2I] in the layouts of `silu_mul`.  act: "silu" (silu(g) u),
+    "relu" (max(g, 0) u) or "capped_swish" (g' = min(g, limit), u' = clamp(u, -limit, limit):
+    g' sigmoid(alpha g') (u' + shift); limit <= 0: none)."""
+    _need(gate_up, None, "gate_up", 2); _need(out, gate_up.dtype, "out", 2)
+    T, I2 = gate_up.shape
+    if I2 % 2 or out.shape != (T, I2 // 2):
+        raise KernelError("gated_act: out must be [T, I] for gate_up [T, 2I]")
+    if act not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation {act!r}; known: {', '.join(ACTIVATIONS)}")
+    _check(_fn("activation", "vl_gated_act")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, int(group),
+                                             ACTIVATIONS[act], float(alpha), float(limit), float(shift), _stream()),
+           "vl_gated_act")
+    return out
+
+
+def scale_softcap(logits, scale, cap):
+    """In place on float32 logits: z <- cap * tanh(z * scale / cap) (cap <= 0 or None: only the scale)."""
+    _need(logits, torch.float32, "logits")
+    _check(_fn("activation", "vl_scale_softcap")(_ptr(logits), logits.numel(), float(scale), float(cap or 0.0), _stream()),
+           "vl_scale_softcap")
+    return logits
+
+
+# ---------------------------------------------------------------- layer norm
+def layernorm_add(y, weight, eps, x, cast=None):
+    """x[r] += layer_norm(y[r]) * weight (no bias; float32 arithmetic); x float32 [T, H], y in the activation
+    dtype.  `cast` (activation dtype, [T, H]) receives the new x."""
+    _need(y, None, "y", 2); _need(weight, torch.float32, "weight", 1); _need(x, torch.float32, "x", 2)
+    if y.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError(f"layernorm_add: shapes disagree: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    if cast is not None:
+        _need(cast, y.dtype, "cast", 2)
+        if cast.shape != x.shape:
+            raise KernelError("layernorm_add: cast must have the stream's shape")
+    _check(_fn("embed_norm", "vl_layernorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(weight), float(eps), _ptr(x), _ptr(cast),
+                                                 x.shape[0], x.shape[1], _stream()), "vl_layernorm_add")
+    return x
+
+
+def layernorm_rows(x, rows, weight, eps, out):
+    """out[r] = layer_norm(x[rows[r]]) * weight (rows None: every row); x float32."""
+    _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1); _need(out, None, "out", 2)
+    R = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+    if out.shape != (R, x.shape[1]) or weight.shape[0] != x.shape[1]:
+        raise KernelError("layernorm_rows: shapes disagree")
+    _check(_fn("embed_norm", "vl_layernorm_rows")(_ptr(x), _ptr(rows), _ptr(weight), float(eps), _ptr(out),
+                                                  dtype_code(out.dtype), R, x.shape[1], _stream()), "vl_layernorm_rows")
+    return out
+
+
+# ---------------------------------------------------------------- latent attention
+def latent_norm_write(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, slots, cache, err):
+    """proj [T, >= q_rank + kv_rank] = [a_q | a_kv]: cq_out [T, q_rank] = rmsnorm(a_q) * q_weight; the cache row
+    `slots[t]` of `cache` [pages, 1, page_size, width >= kv_rank] = rmsnorm(a_kv) * kv_weight, zero beyond kv_rank
+    (slots None or negative: no write)."""
+    _need(proj, None, "proj", 2); _need(cq_out, proj.dtype, "cq_out", 2)
+    _need(q_weight, torch.float32, "q_weight", 1); _need(kv_weight, torch.float32, "kv_weight", 1)
+    T = proj.shape[0]
+    if proj.shape[1] < q_rank + kv_rank or cq_out.shape != (T, q_rank) or q_weight.shape[0] != q_rank \
+            or kv_weight.shape[0] != kv_rank:
+        raise KernelError("latent_norm_write: shapes disagree")
+    width, num_slots = kv_rank, 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots", 1); _need(cache, proj.dtype, "cache", 4)
+        if cache.shape[1] != 1 or cache.shape[3] < kv_rank or slots.shape[0] < T:
+            raise KernelError(f"latent_norm_write: cache {tuple(cache.shape)} does not hold rows of {kv_rank}")
+        width, num_slots = cache.shape[3], cache.shape[0] * cache.shape[2]
+    _check(_fn("latent", "vl_latent_norm_write")(
+        _ptr(proj), dtype_code(proj.dtype), proj.shape[1], T, int(q_rank), int(kv_rank), _ptr(q_weight), _ptr(kv_weight),
+        float(eps), _ptr(cq_out), _ptr(slots), _ptr(cache) if slots is not None else None, width, num_slots,
+        _ptr(err), _stream()), "vl_latent_norm_write")
+    return cq_out
+
+
+def gemm_heads(a, w, out):
+    """One product per head on column slices: a [T, H*K], w [H, N, K], out [T, H*N];
+    out[:, h*N:(h+1)*N] = a[:, h*K:(h+1)*K] @ w[h]^T.  float32 accumulation in a fixed order over K."""
+    _need(a, None, "a", 2); _need(w, a.dtype, "w", 3); _need(out, a.dtype, "out", 2)
+    H, N, K = w.shape
+    T = a.shape[0]
+    if a.shape[1] != H * K or out.shape != (T, H * N):
+        raise KernelError(f"gemm_heads: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("gemm_batched", "vl_gemm_batched_nt")(
+        _ptr(a), _ptr(w), _ptr(out), dtype_code(a.dtype), T, N, K, H * K, K, H * N, K, N * K, N, H, None, 0,
+        16 if T <= 16 else 64, _stream()), "vl_gemm_batched_nt")
+    return out
+
+
+def gemm_grouped(rows, w, out, tile_group, bm):
+    """rows [cap, K] sorted by group in tiles of `bm` rows (`moe_align`), w [G, N, K], out [cap, N]:
+    tile y is multiplied by w[tile_group[y]]; tiles with a negative group are skipped."""
+    _need(rows, None, "rows", 2); _need(w, rows.dtype, "w", 3); _need(out, rows.dtype, "out", 2)
+    _need(tile_group, torch.int32, "tile_group", 1)
+    G, N, K = w.shape
+    cap = rows.shape[0]
+    if rows.shape[1] != K or out.shape != (cap, N) or cap % bm or tile_group.shape[0] < cap // bm:
+        raise KernelError("gemm_grouped: shapes disagree")
+    _check(_fn("gemm_batched", "vl_gemm_batched_nt")(
+        _ptr(rows), _ptr(w), _ptr(out), dtype_code(rows.dtype), cap, N, K, K, K, N, 0, 0, 0, 1, _ptr(tile_group), N * K,
+        int(bm), _stream()), "vl_gemm_batched_nt")
+    return out
+
+
+# ---------------------------------------------------------------- routed experts
+ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_sorted_rows(npairs, num_experts, bm) -> int:
+    """Rows of the buffers that hold `npairs` (token, choice) pairs sorted by expert in tiles of bm rows."""
+    need = npairs + min(num_experts, npairs) * (bm - 1)
+    return -(-need // bm) * bm
+
+
+def moe_route(h, router, top, ids, weights, score="sigmoid", renormalize=False):
+    """h [T, K], router float32 [E, K]: ids int32 [T, top] = the experts with the largest scores,
+    weights float32 [T, top] = their scores (divided by their sum when `renormalize`)."""
+    _need(h, None, "h", 2); _need(router, torch.float32, "router", 2)
+    _need(ids, torch.int32, "ids", 2); _need(weights, torch.float32, "weights", 2)
+    T, K = h.shape
+    E = router.shape[0]
+    if router.shape[1] != K or ids.shape != (T, top) or weights.shape != (T, top):
+        raise KernelError("moe_route: shapes disagree")
+    _check(_fn("moe", "vl_moe_route")(_ptr(h), dtype_code(h.dtype), _ptr(router), T, E, K, int(top), ROUTER_SCORES[score],
+                                      int(bool(renormalize)), _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
+
+
+def moe_align(ids, num_experts, bm, sorted_rows, tile_group, place):
+    _need(ids, torch.int32, "ids"); _need(sorted_rows, torch.int32, "sorted_rows", 1)
+    _need(tile_group, torch.int32, "tile_group", 1); _need(place, torch.int32, "place", 1)
+    n, cap = ids.numel(), sorted_rows.shape[0]
+    if cap != moe_sorted_rows(n, num_experts, bm) or tile_group.shape[0] < cap // bm or place.shape[0] < n:
+        raise KernelError("moe_align: buffer sizes do not match the number of pairs")
+    _check(_fn("moe", "vl_moe_align")(_ptr(ids), n, int(num_experts), int(bm), cap, _ptr(sorted_rows), _ptr(tile_group),
+                                      _ptr(place), _stream()), "vl_moe_align")
+
+
+def moe_gather(h, sorted_rows, weights, top, rows, scale_input):
+    _need(h, None, "h", 2); _need(rows, h.dtype, "rows", 2); _need(weights, torch.float32, "weights")
+    if rows.shape != (sorted_rows.shape[0], h.shape[1]):
+        raise KernelError("moe_gather: shapes disagree")
+    _check(_fn("moe", "vl_moe_gather")(_ptr(h), dtype_code(h.dtype), _ptr(sorted_rows), _ptr(weights), rows.shape[0],
+                                       int(top), h.shape[1], int(bool(scale_input)), _ptr(rows), _stream()), "vl_moe_gather")
+    return rows
+
+
+def moe_combine(result, place, weights, top, out, scale_output):
+    _need(result, None, "result", 2); _need(out, result.dtype, "out", 2); _need(weights, torch.float32, "weights")
+    T, N = out.shape
+    if result.shape[1] != N or place.shape[0] < T * top:
+        raise KernelError("moe_combine: shapes disagree")
+    _check(_fn("moe", "vl_moe_combine")(_ptr(result), dtype_code(result.dtype), _ptr(place), _ptr(weights), T, int(top), N,
+                                        int(bool(scale_output)), _ptr(out), _stream()), "vl_moe_combine")
     return out
 
 

@@ -27,7 +27,7 @@ def load_model_dir(model_dir, dtype, device):
     """(typed configuration, plan, {name: device tensor})."""
     dtype = parse_dtype(dtype)
     cfg, plan = plan_from_config_json(read_config_json(model_dir))
-    weights = load_weights(model_dir, declare_model(plan), dtype, device)
+    weights = load_weights(model_dir, declare_model(plan), dtype, device, unused=plan.unused_tensors)
     return cfg, plan, weights
 
 

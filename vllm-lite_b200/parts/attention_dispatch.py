@@ -48,10 +48,16 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
                             arrivals=arrivals, fold=fold)
 
 
-def run(qkv, out, cache, group, step, spec, scale, fold=None):
-    """`fold` (only where `folds_head_work` said so): (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) of the
-    head work that the mixer left undone."""
+def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None):
+    """`spec`: anything with num_heads, num_kv_heads, head_dim and window.
+    `fold` (only where `folds_head_work` said so): (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) of the
+    head work that the mixer left undone.
+    `sinks` (float32 [num_heads]): a number per head that joins every softmax denominator as exp(sink)."""
     from ..csrc import ops
+    if sinks is not None:
+        args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
+                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
+        return ops.paged_attention(*args, step.err, sinks=sinks)
     if fold is not None and not folds_head_work(qkv.dtype, step, spec, group, qkv.shape[0]):
         raise ValueError("this step's attention kernel does not fold the head norm and rotation in")
     args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,

@@ -134,6 +134,7 @@ class Residual:
     pending: Optional[torch.Tensor] = None    # not yet added into x
     normed: Optional["ScaledRows"] = None     # output of the norm `normed_for` on x, in factored form
     normed_for: object = None
+    cast: Optional[torch.Tensor] = None       # x in the activation dtype, when the kernel that last wrote x left it
 
 
 @dataclass

@@ -9,6 +9,8 @@ leaves the norm's output in factored form (`ScaledRows`), which the part after
 the norm takes as it is."""
 from __future__ import annotations
 
+import torch
+
 from .base import StreamSink, prefixed, sub_weights
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .spec import BlockSpec
@@ -49,6 +51,7 @@ class PreNormBlock:
         """next_norm: the norm that will read the stream after this block, when its reader can take
         the factored form (`input_norm_for_fusion` of the next block)."""
         M = step.num_tokens
+        residual.cast = None                                      # this block's kernels write x without it
         if residual.normed is not None and residual.normed_for is self.norm1:
             h = residual.normed                                   # left by the block before
         else:
@@ -73,3 +76,70 @@ def _factors(part, M) -> bool:
 
 def _sink(residual, norm) -> StreamSink:
     return StreamSink(residual.x, norm.weight, norm.spec.eps, norm.spec.size)
+
+
+@BLOCKS.register("post_norm")
+class PostNormBlock:
+    """x += norm1(mixer(x)); x += norm2(ffn(x)): the norms sit on the sub-layers' outputs and the sub-layers
+    read the stream itself (its rounding to the activation dtype).  The norm's kernel adds its result into
+    the float32 stream and leaves the new stream in the activation dtype for the next sub-layer.  A block
+    without a feed-forward (`spec.ffn` None) is its first half alone."""
+
+    @staticmethod
+    def declare(spec: BlockSpec) -> dict:
+        norm1, mixer, norm2, ffn = spec.names
+        d = {}
+        d.update(prefixed(NORMS.get(spec.norm1.kind).declare(spec.norm1), norm1))
+        d.update(prefixed(MIXERS.get(spec.mixer.kind).declare(spec.mixer), mixer))
+        if spec.ffn is not None:
+            d.update(prefixed(NORMS.get(spec.norm2.kind).declare(spec.norm2), norm2))
+            d.update(prefixed(FEED_FORWARDS.get(spec.ffn.kind).declare(spec.ffn), ffn))
+        return d
+
+    @staticmethod
+    def cache_need(spec: BlockSpec):
+        return MIXERS.get(spec.mixer.kind).cache_need(spec.mixer)
+
+    def __init__(self, spec: BlockSpec, weights: dict, ctx):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        norm1, mixer, norm2, ffn = spec.names
+        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, _exact(weights, norm1, spec.norm1), ctx)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, mixer), ctx)
+        self.norm2 = self.ffn = None
+        if spec.ffn is not None:
+            self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, _exact(weights, norm2, spec.norm2), ctx)
+            self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, ffn), ctx)
+        for norm in (self.norm1, self.norm2):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise TypeError(f"norm kind {norm.spec.kind!r} cannot norm a sub-layer's output into the stream: "
+                                f"it offers no add_normed(y, x, step, cast)")
+        self.graph_safe = bool(getattr(self.mixer, "graph_safe", False)
+                               and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    def _stream_input(self, residual, step):
+        if residual.pending is not None or residual.normed is not None:
+            raise NotImplementedError("a post-norm block after a block that leaves its result pending")
+        if self.dtype == torch.float32:
+            return residual.x, None
+        buf = step.workspace.get(step.tag + "stream.cast", residual.x.shape, self.dtype)
+        if residual.cast is None:
+            from ..csrc import ops
+            residual.cast = ops.cast(residual.x, buf)
+        return residual.cast, buf
+
+    def __call__(self, residual, step, cache):
+        h, buf = self._stream_input(residual, step)
+        y = self.mixer(h, step, cache)
+        residual.cast = self.norm1.add_normed(y, residual.x, step, buf)
+        if self.ffn is not None:
+            h = residual.x if buf is None else residual.cast
+            y = self.ffn(h, step)
+            residual.cast = self.norm2.add_normed(y, residual.x, step, buf)
+
+
+def _exact(weights, prefix, norm_spec):
+    """The tensors of a norm whose prefix may be its weight's whole name (`tensor` == "")."""
+    if getattr(norm_spec, "tensor", "weight") == "":
+        return {"": weights[prefix]} if prefix in weights else {}
+    return sub_weights(weights, prefix)

@@ -19,11 +19,11 @@ class TokenEmbedding:
 
     @staticmethod
     def declare(spec: EmbeddingSpec) -> dict:
-        return {"weight": TensorDecl((spec.vocab_size, spec.hidden_size))}
+        return {spec.tensor: TensorDecl((spec.vocab_size, spec.hidden_size))}
 
     def __init__(self, spec: EmbeddingSpec, weights: dict, ctx):
         self.spec = spec
-        self.table = weights["weight"]
+        self.table = weights[spec.tensor]
 
     def tied_weight(self):
         return self.table

@@ -1,0 +1,76 @@
+"""Routed experts: every token is sent through `top` of `num_experts` small gated feed-forwards.
+
+    z = W_r h (float32), score = sigmoid(z) or softmax(z); the `top` largest scores choose the experts
+    out = sum_e E_e(w_e h)            (`scale_input`: the weight multiplies the expert's INPUT)
+       or sum_e w_e E_e(h)
+    E(y) = W_down (f(W_gate y, W_up y)),  f as in `ops.gated_act` (for "capped_swish":
+           g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + up_shift))
+
+No host decision anywhere, so a step stays a fixed sequence of launches (and a decode step a CUDA graph):
+the router kernel writes ids and weights, one block sorts the (token, choice) pairs by expert into tiles
+of rows (every expert's rows padded to whole tiles), a gather kernel lays the (scaled) inputs out in that
+order, two grouped products with the activation between them run over the tiles, each tile with its
+expert's matrices, and a last kernel sums a token's results in the order of its choices.  A row's
+arithmetic does not depend on where it was sorted to, so logits do not depend on the batch.
+"""
+from __future__ import annotations
+
+import torch
+
+from .registry import FEED_FORWARDS
+from .spec import RoutedExpertsSpec, TensorDecl
+
+SMALL_STEP_PAIRS = 64       # up to this many (token, choice) pairs the tiles hold 16 rows, else 64
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts:
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: RoutedExpertsSpec) -> dict:
+        gate, up, down = spec.names
+        I, H = spec.intermediate_size, spec.hidden_size
+        d = {spec.router: TensorDecl((spec.num_experts, H))}
+        for e in range(spec.num_experts):
+            p = spec.expert_prefix.format(e)
+            d.update({p + gate: TensorDecl((I, H)), p + up: TensorDecl((I, H)), p + down: TensorDecl((H, I))})
+        return d
+
+    def __init__(self, spec: RoutedExpertsSpec, weights: dict, ctx):
+        from ..csrc import ops
+        if not 0 < spec.top <= spec.num_experts:
+            raise ValueError(f"routed experts: top {spec.top} of {spec.num_experts} experts")
+        if spec.activation not in ops.ACTIVATIONS or spec.score not in ops.ROUTER_SCORES:
+            raise ValueError(f"routed experts: activation {spec.activation!r} / score {spec.score!r} not known")
+        self.spec = spec
+        self.dtype = ctx.dtype
+        gate, up, down = spec.names
+        E = spec.num_experts
+        names = [spec.expert_prefix.format(e) for e in range(E)]
+        # the router works in float32 whatever the model's dtype (exact from bfloat16)
+        self.router = weights[spec.router].to(device=ctx.device, dtype=torch.float32).contiguous()
+        # per expert [gate rows; up rows], stacked over experts: [E, 2I, H]; down: [E, H, I]
+        self.gate_up = torch.stack([torch.cat([weights[p + gate], weights[p + up]], dim=0) for p in names]).contiguous()
+        self.down = torch.stack([weights[p + down] for p in names]).contiguous()
+
+    def __call__(self, h, step):
+        from ..csrc import ops
+        s, ws, tag = self.spec, step.workspace, step.tag
+        T, E, top, I, H = h.shape[0], s.num_experts, s.top, s.intermediate_size, s.hidden_size
+        pairs = T * top
+        bm = 16 if pairs <= SMALL_STEP_PAIRS else 64
+        cap = ops.moe_sorted_rows(pairs, E, bm)
+        ids = ws.get(tag + "moe.ids", (T, top), torch.int32)
+        weights = ws.get(tag + "moe.weights", (T, top), torch.float32)
+        sorted_rows = ws.get(tag + "moe.sorted", (cap,), torch.int32)
+        tile_group = ws.get(tag + "moe.tiles", (cap // bm,), torch.int32)
+        place = ws.get(tag + "moe.place", (pairs,), torch.int32)
+        ops.moe_route(h, self.router, top, ids, weights, s.score, s.renormalize)
+        ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
+        rows = ops.moe_gather(h, sorted_rows, weights, top, ws.get(tag + "moe.rows", (cap, H), self.dtype), s.scale_input)
+        gu = ops.gemm_grouped(rows, self.gate_up, ws.get(tag + "moe.gate_up", (cap, 2 * I), self.dtype), tile_group, bm)
+        act = ops.gated_act(gu, ws.get(tag + "moe.act", (cap, I), self.dtype), s.activation, 0, s.alpha, s.limit, s.up_shift)
+        res = ops.gemm_grouped(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, bm)
+        out = ws.get(tag + "moe.out", (T, H), self.dtype)
+        return ops.moe_combine(res, place, weights, top, out, not s.scale_input)

@@ -1,0 +1,49 @@
+"""Gated feed-forward with a choice of activation and optional biases:
+down(act(gate(h) + b_g) * (up(h) + b_u)) + b_d, act = "silu" or "relu".
+
+gate and up are stacked into one matrix (gate rows, then up rows) so that one product serves both;
+the biases are added in float32 by the linear layer, the activation is one kernel on the stacked result.
+The SwiGLU part (`parts/mlp.py`) is the bias-free special case whose activation the product kernels
+fuse; this part serves what that one does not take."""
+from __future__ import annotations
+
+import torch
+
+from .linear import Linear
+from .registry import FEED_FORWARDS
+from .spec import GatedMlpSpec, TensorDecl
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMlp:
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: GatedMlpSpec) -> dict:
+        gate, up, down = spec.names
+        I, H = spec.intermediate_size, spec.hidden_size
+        d = {gate: TensorDecl((I, H)), up: TensorDecl((I, H)), down: TensorDecl((H, I))}
+        if spec.bias:
+            d.update({gate + spec.bias_suffix: TensorDecl((I,)), up + spec.bias_suffix: TensorDecl((I,)),
+                      down + spec.bias_suffix: TensorDecl((H,))})
+        return d
+
+    def __init__(self, spec: GatedMlpSpec, weights: dict, ctx):
+        from ..csrc import ops
+        if spec.activation not in ("silu", "relu"):
+            raise ValueError(f"gated_mlp: activation {spec.activation!r}; known: silu, relu")
+        assert spec.activation in ops.ACTIVATIONS
+        self.spec = spec
+        self.dtype = ctx.dtype
+        gate, up, down = spec.names
+        b = spec.bias_suffix
+        bias = torch.cat([weights[gate + b].float(), weights[up + b].float()], dim=0) if spec.bias else None
+        self.gate_up = Linear(torch.cat([weights[gate], weights[up]], dim=0).contiguous(), bias)
+        self.down = Linear(weights[down], weights[down + b].float() if spec.bias else None)
+
+    def __call__(self, h, step):
+        from ..csrc import ops
+        gu = self.gate_up(h, step, "mlp.gate_up")
+        act = step.workspace.get(step.tag + "mlp.act", (gu.shape[0], self.spec.intermediate_size), gu.dtype)
+        ops.gated_act(gu, act, self.spec.activation)
+        return self.down(act, step, "mlp.down")

@@ -12,7 +12,7 @@ import torch
 
 from .linear import Linear
 from .registry import HEADS
-from .spec import HeadSpec, TensorDecl
+from .spec import CappedHeadSpec, HeadSpec, TensorDecl
 
 
 @HEADS.register("linear_head")
@@ -35,3 +35,22 @@ class LinearHead:
 
     def __call__(self, h, step):
         return self.proj(h, step, "logits", out_dtype=torch.float32)
+
+
+@HEADS.register("capped_head")
+class CappedHead:
+    """logits = cap * tanh((h W^T) * scale / cap): the product in float32 accumulation, then one kernel in place."""
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: CappedHeadSpec) -> dict:
+        return {spec.tensor: TensorDecl((spec.vocab_size, spec.hidden_size))}
+
+    def __init__(self, spec: CappedHeadSpec, weights: dict, ctx, embedding=None):
+        self.spec = spec
+        self.proj = Linear(weights[spec.tensor])
+
+    def __call__(self, h, step):
+        from ..csrc import ops
+        logits = self.proj(h, step, "logits", out_dtype=torch.float32)
+        return ops.scale_softcap(logits, self.spec.scale, self.spec.softcap)

@@ -15,13 +15,13 @@ class RmsNorm:
 
     @staticmethod
     def declare(spec: NormSpec) -> dict:
-        return {"weight": TensorDecl((spec.size,), init="norm")}
+        return {spec.tensor: TensorDecl((spec.size,), init="norm")}
 
     def __init__(self, spec: NormSpec, weights: dict, ctx):
         self.spec = spec
         self.dtype = ctx.dtype
         # A vector of `size` numbers: kept as float32 on the device (exact from bfloat16).
-        self.weight = weights["weight"].to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.weight = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32).contiguous()
 
     def fused_rms(self):
         """(weight, eps): what a kernel that applies this norm itself needs (the attention mixer's
@@ -33,3 +33,33 @@ class RmsNorm:
         R = x.shape[0] if rows is None else rows.shape[0]
         out = step.workspace.get(step.tag + tag, (R, self.spec.size), self.dtype)
         return ops.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows=rows)
+
+
+@NORMS.register("layer_norm")
+class LayerNorm:
+    """h = (x - mean x) / sqrt(var x + eps) * w, var = the mean of the squared deviations, no bias; float32.
+    Beside the interface of every norm (`__call__`: the stream's rows, a pending delta added first) it offers
+    `add_normed`, what a block that norms its sub-layers' outputs calls."""
+
+    @staticmethod
+    def declare(spec: NormSpec) -> dict:
+        return {spec.tensor: TensorDecl((spec.size,), init="norm")}
+
+    def __init__(self, spec: NormSpec, weights: dict, ctx):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        self.weight = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32).contiguous()
+
+    def add_normed(self, y, x, step, cast=None):
+        """x += norm(y); `cast` (a buffer in the activation dtype, or None) receives the new x.  Returns cast."""
+        from ..csrc import ops
+        ops.layernorm_add(y, self.weight, self.spec.eps, x, cast)
+        return cast
+
+    def __call__(self, x, delta, step, rows=None, tag="norm"):
+        from ..csrc import ops
+        if delta is not None:
+            raise NotImplementedError("the layer norm takes the stream as it is; a pending delta belongs to a pre-norm block")
+        R = x.shape[0] if rows is None else rows.shape[0]
+        out = step.workspace.get(step.tag + tag, (R, self.spec.size), self.dtype)
+        return ops.layernorm_rows(x, rows, self.weight, self.spec.eps, out)

@@ -33,9 +33,12 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """`kind`: "rms_norm" (x / sqrt(mean x^2 + eps) * w) or "layer_norm" ((x - mean) / sqrt(var + eps) * w,
+    no bias).  `tensor`: the weight's name relative to the norm's prefix ("" when the prefix is the whole name)."""
     size: int
     eps: float
     kind: str = "rms_norm"
+    tensor: str = "weight"
 
 
 @dataclass(frozen=True)
@@ -79,6 +82,7 @@ class EmbeddingSpec:
     vocab_size: int
     hidden_size: int
     kind: str = "token_embedding"
+    tensor: str = "weight"          # the table's name relative to the embedding's prefix
 
 
 @dataclass(frozen=True)
@@ -92,6 +96,81 @@ class HeadSpec:
 
 
 @dataclass(frozen=True)
+class CappedHeadSpec:
+    """logits = cap * tanh((h W^T) * scale / cap) in float32, W a matrix of the head's own; `softcap` None: only
+    the scale."""
+    vocab_size: int
+    hidden_size: int
+    scale: float = 1.0
+    softcap: Optional[float] = None
+    tensor: str = "weight"
+    kind: str = "capped_head"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are both expanded from one cached latent row per token.
+
+    c_q = rmsnorm(W_dq h), q = W_uq c_q (heads x dim); c = rmsnorm(W_dkv h) (kv_rank, the cached row);
+    k_h = W_uk[h] c (dim), v_h = W_uv[h] c (vdim); scores scale * q.k over the last `window` positions
+    (None: all earlier ones); `sink`: a learned number per head joins every softmax denominator;
+    out = W_o concat_h(sum p v).  No position encoding.  `names`: the tensors' names relative to the mixer's
+    prefix, in the order (dq, dq norm, uq, dkv, dkv norm, uk, uv, o, sink)."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    eps: float
+    scale: Optional[float] = None
+    window: Optional[int] = None
+    sink: bool = False
+    names: Tuple[str, ...] = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "o", "sink")
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class GatedMlpSpec:
+    """down(act(gate(h)) * up(h)) with a choice of activation ("silu", "relu") and optional bias vectors on all
+    three projections.  `names`: (gate, up, down) relative to the part's prefix; a bias is `<name><bias_suffix>`."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "silu"
+    bias: bool = False
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+    bias_suffix: str = ".b"
+    kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of small gated feed-forwards of which every token uses `top`.
+
+    Router: z = W_r h in float32, score = sigmoid(z) ("sigmoid") or softmax(z) ("softmax"); the `top`
+    largest scores choose; weights are the chosen scores, divided by their sum when `renormalize`.
+    `scale_input`: the weight multiplies the expert's input (out = sum_e E_e(w_e h)), else its output.
+    Expert: g = gate y, u = up y, no biases; activation "capped_swish": g' = min(g, limit),
+    u' = clamp(u, -limit, limit), down(g' sigmoid(alpha g') (u' + up_shift)); "silu" / "relu": down(act(g) u).
+    Tensors: `router`, and per expert i `expert_prefix.format(i)` + gate / up / down of `names`."""
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    top: int
+    activation: str = "capped_swish"
+    alpha: float = 1.702
+    limit: float = 0.0
+    up_shift: float = 1.0
+    score: str = "sigmoid"
+    renormalize: bool = False
+    scale_input: bool = True
+    router: str = "router"
+    expert_prefix: str = "e{}."
+    names: Tuple[str, str, str] = ("gate", "up", "down")
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class SwiGLUSpec:
     hidden_size: int
     intermediate_size: int
@@ -100,7 +179,9 @@ class SwiGLUSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """Pre-norm residual block: x += mixer(norm1(x)); x += ffn(norm2(x))."""
+    """kind "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)).
+    kind "post_norm": x += norm1(mixer(x)); x += norm2(ffn(x)): the sub-layers read the stream itself and
+    their OUTPUTS are normed; `ffn` may be None (the block is then its mixer alone, and norm2 is unused)."""
     mixer: object
     ffn: object
     norm1: NormSpec
@@ -143,6 +224,8 @@ class ModelPlan:
     # they are the plain ones, described by vocab_size, hidden_size and tie_word_embeddings.
     embedding: Optional[object] = None
     head: Optional[object] = None
+    # names of stored tensors that the model does not bind and that the loader passes over
+    unused_tensors: Tuple[str, ...] = ()
 
     @property
     def embedding_spec(self):

@@ -56,8 +56,9 @@ def find_weight_files(model_dir):
     return shards
 
 
-def load_weights(model_dir, declared: dict, dtype: torch.dtype, device) -> dict:
-    """{name: device tensor} for every declared tensor; raises WeightError otherwise."""
+def load_weights(model_dir, declared: dict, dtype: torch.dtype, device, unused=()) -> dict:
+    """{name: device tensor} for every declared tensor; raises WeightError otherwise.  `unused`: names
+    that the folder may hold without the model binding them (they are passed over, not read)."""
     files, where, other = [], {}, []
     for path in find_weight_files(model_dir):
         try:
@@ -72,7 +73,7 @@ def load_weights(model_dir, declared: dict, dtype: torch.dtype, device) -> dict:
                 other.append(f"duplicate tensor {name} in {where[name].path.name} and {f.path.name}")
             where[name] = f
     missing = [n for n in declared if n not in where]
-    unexpected = [n for n in where if n not in declared]
+    unexpected = [n for n in where if n not in declared and n not in unused]
     wrong_shape, wrong_dtype = [], []
     for name, decl in declared.items():
         if name not in where:
