@@ -43,18 +43,15 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, int ntok
         if (lane == 0) sc[e] = acc;
     }
     __syncwarp();
+    // The choice is made on the logits: both score functions grow with z, and a sigmoid that has
+    // rounded to 1 for several experts would hide which of them is the largest.
+    float zmax = -INFINITY, zsum = 0.f;
     if (score_fn == MOE_SCORE_SOFTMAX) {
-        float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
-        m = warp_max(m);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) sum += expf(sc[e] - m);
-        sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - m) / sum;
-    } else {
-        for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, sc[e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < E; e += 32) zsum += expf(sc[e] - zmax);
+        zsum = warp_sum(zsum);
     }
-    __syncwarp();
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
@@ -69,12 +66,13 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, int ntok
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
+        const float score = score_fn == MOE_SCORE_SOFTMAX ? expf(best - zmax) / zsum : 1.0f / (1.0f + expf(-best));
         if (lane == 0) {
             ids[(size_t)t * top + j] = arg;
-            weights[(size_t)t * top + j] = best;
+            weights[(size_t)t * top + j] = score;
             sc[arg] = -INFINITY;
         }
-        total += best;
+        total += score;
         __syncwarp();
     }
     if (renorm && lane == 0)
