@@ -466,7 +466,7 @@ template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
                                               int nq, int hd, int chunk, int S, int window,
-                                              const int* __restrict__ token_index) {
+                                              const int* __restrict__ token_index, const float* __restrict__ sinks) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;                    // t numbers the tokens of the launch
@@ -489,7 +489,11 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc
         const float ms = part_ml[(row0 + s) * 2];
         L += (ms == -INFINITY) ? 0.f : part_ml[(row0 + s) * 2 + 1] * att_exp<T>(ms - M);
     }
-    const float invL = L > 0.f ? 1.0f / L : 0.f;
+    float invL = L > 0.f ? 1.0f / L : 0.f;
+    if (sinks) {                                                 // one more term exp(sink_h) in the denominator
+        const float sk = sinks[h], Mx = fmaxf(M, sk), a = expf(M - Mx);
+        invL = a / (L * a + expf(sk - Mx));
+    }
     for (int e = threadIdx.x; e < hd; e += blockDim.x) {
         float o = 0.f;
         for (int s = s0; s <= s1; ++s) {
@@ -555,22 +559,22 @@ static int decode_attention_typed(const T* q, int q_stride, T* out, const T* kc,
     }
 #undef DEC_PASS
     if (rc != 0) return rc;
-    decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window, nullptr);
+    decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window, nullptr, nullptr);
     return vl_launch_status();
 }
 
 // Merges per-chunk partial results (of vl_decode_attention's first pass or of vl_flash_decode).
 extern "C" int vl_decode_attention_merge(const float* part_acc, const float* part_ml, const int* positions, void* out,
                                          int dtype, int T, int nq, int hd, int chunk, int S, int window,
-                                         const int* token_index, void* stream) {
+                                         const int* token_index, const float* sinks, void* stream) {
     if (T <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(decode_attention_merge_kernel<float>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
-                         (float*)out, nq, hd, chunk, S, window, token_index);
+                         (float*)out, nq, hd, chunk, S, window, token_index, sinks);
     if (dtype == VL_BF16)
         return vl_launch(decode_attention_merge_kernel<bf16>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
-                         (bf16*)out, nq, hd, chunk, S, window, token_index);
+                         (bf16*)out, nq, hd, chunk, S, window, token_index, sinks);
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -96,13 +96,23 @@ __device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf
 }
 }  // namespace
 
+// A softmax with a sink has one more term 2^sink in its denominator (sink in units of log2, not scaled, no key and
+// no value).  For a row whose sums are relative to the maximum m (log2 units) and add up to l, this is the
+// factor that turns the accumulated output into the result: 2^(m - M) / (l 2^(m - M) + 2^(sink - M)), M = max(m, sink).
+__device__ __forceinline__ float sink_inverse_log2(float m, float l, float sink) {
+    if (m == -INFINITY) return 0.f;
+    const float M = fmaxf(m, sink), a = exp2f(m - M);
+    return a / (l * a + exp2f(sink - M));
+}
+
 // tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first};
 // blocks (h, y) serve head h and, of the list walked from its end, the tokens 64 * (y' % parts) ... of tile y' / parts
 extern "C" __global__ void __launch_bounds__(NTHREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                      const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int parts,
-                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err) {
+                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err,
+                     const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
@@ -247,7 +257,12 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    if (sinks) {                                                 // one more term exp(sink_h) in the denominator
+        const float sk = sinks[h] * 1.4426950408889634f;
+        inv_a = sink_inverse_log2(m_run[0], l_run[0], sk);
+        inv_b = sink_inverse_log2(m_run[1], l_run[1], sk);
+    }
     if (row_a) {
         bf16* op = out + ((size_t)(tok0 + row0 + g) * nq + h) * HD + 2 * t;
 #pragma unroll
@@ -265,7 +280,7 @@ extern "C" int vl_flash_head_dim() { return HD; }
 extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
                                 const int* block_table, int max_blocks, const int* tiles, int num_tiles, int tile_rows,
                                 int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                                unsigned* err, void* stream) {
+                                unsigned* err, const float* sinks, void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
@@ -277,7 +292,7 @@ extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const vo
     if (e != cudaSuccess) return (int)e;
     flash_prefill_kernel<<<dim3(nq, num_tiles * parts), NTHREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
-        (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
+        (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks);
     return vl_launch_status();
 }
 
@@ -314,7 +329,8 @@ constexpr int DEC_MAX_CLUSTER = 16;                  // most chunks of a token t
 // the S merges an S-th of the elements, the chunks in their order, through the cluster's shared
 // window, and writes them to the output rows.
 __device__ __forceinline__ void decode_cluster_merge(const float* bO, const float* bM, const float* bL, bf16* out,
-                                                     int tok, int nq, int h0, int nvalid, int S, int rank, int tid) {
+                                                     int tok, int nq, int h0, int nvalid, int S, int rank, int tid,
+                                                     const float* sinks) {
     __syncthreads();
     dec_cluster_sync();
     unsigned aO[DEC_MAX_CLUSTER], aM[DEC_MAX_CLUSTER], aL[DEC_MAX_CLUSTER];
@@ -346,7 +362,8 @@ __device__ __forceinline__ void decode_cluster_merge(const float* bO, const floa
             L += l[s] * wgt;
             acc += a[s] * wgt;
         }
-        out[((size_t)tok * nq + h0 + r) * HD + (idx - r * HD)] = __float2bfloat16(acc * (L > 0.f ? 1.0f / L : 0.f));
+        const float inv = sinks ? sink_inverse_log2(M, L, sinks[h0 + r] * 1.4426950408889634f) : (L > 0.f ? 1.0f / L : 0.f);
+        out[((size_t)tok * nq + h0 + r) * HD + (idx - r * HD)] = __float2bfloat16(acc * inv);
     }
     dec_cluster_sync();                                          // no block leaves while another may still read its result
 }
@@ -365,6 +382,7 @@ struct DecodeFusion {
     const int* slots; long long num_slots;               // cache slot of every token of the step
     bf16* kcache; bf16* vcache;                          // the cache again, to write
     int on;
+    const float* sinks;                                  // (any launch) a sink per query head for the softmax, or null
 };
 
 // TR: the products are taken the other way round, S^T = K Q^T and O^T = V^T P^T: the 16 keys of a warp's tile are
@@ -427,7 +445,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         pdl_wait();                                              // the merge writes output rows
         for (int i = tid; i < nvalid * HD; i += NTHREADS) bO[i] = 0.f;
         if (tid < DEC_ROWS) { s_bm[tid] = -INFINITY; s_bl[tid] = 0.f; }
-        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid);
+        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, fz.sinks);
         return;
     }
     const int* table = block_table + (size_t)req_index[tok] * max_blocks;
@@ -711,7 +729,9 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             L += s_l[w][r] * wgt;
         }
         if (alone) {                                             // nothing to merge with: the output row itself
-            out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * (L > 0.f ? 1.0f / L : 0.f));
+            const float inv = fz.sinks ? sink_inverse_log2(M, L, fz.sinks[h0 + r] * 1.4426950408889634f)
+                                       : (L > 0.f ? 1.0f / L : 0.f);
+            out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * inv);
             continue;
         }
         if (in_cluster) {
@@ -728,7 +748,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     }
     if (alone) return;
     if (in_cluster) {
-        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid);
+        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, fz.sinks);
         return;
     }
     if (!arrivals) return;                                       // the caller merges with a kernel of its own
@@ -772,7 +792,13 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         L += __shfl_xor_sync(0xffffffffu, L, 1);
         L += __shfl_xor_sync(0xffffffffu, L, 2);
         L += __shfl_xor_sync(0xffffffffu, L, 4);
-        if (part == 0) s_inv[r] = L > 0.f ? 1.0f / L : 0.f;
+        if (part == 0) {
+            s_inv[r] = L > 0.f ? 1.0f / L : 0.f;
+            if (fz.sinks) {                                      // natural-log units here
+                const float sk = fz.sinks[h0 + min(r, nvalid - 1)], Mx = fmaxf(M, sk), a = __expf(M - Mx);
+                s_inv[r] = a / (L * a + __expf(sk - Mx));
+            }
+        }
     }
     __syncthreads();
     for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
@@ -896,8 +922,9 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
                                const int* block_table, int max_blocks, const int* req_index, const int* positions,
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
-                               const int* token_index, void* out, int* arrivals, void* stream) {
+                               const int* token_index, void* out, int* arrivals, const float* sinks, void* stream) {
     DecodeFusion fz = {};
+    fz.sinks = sinks;
     return launch_flash_decode(q, q_stride, kcache, vcache, block_table, max_blocks, req_index, positions, T, nq, nkv, hd,
                                page_size, num_pages, scale, window, chunk, S, part_acc, part_ml, err, token_index, out,
                                arrivals, fz, stream);

@@ -111,7 +111,8 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                  const __grid_constant__ CUtensorMap pages_k, const __grid_constant__ CUtensorMap pages_v, int use_pages,
                  const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                  const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int num_tiles,
-                 int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err) {
+                 int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err,
+                 const float* __restrict__ sinks) {
     // tiles of the 128-byte swizzle must start on 1024-byte boundaries; there is no static shared
     // memory in this kernel, so the array starts the block's window
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -370,7 +371,13 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         }
         if (ok && __all_sync(0xffffffffu, mbar_wait_bounded(&pv_done, (unsigned)((n_tiles - 1) & 1)))) {
             tc5_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            float inv = l > 0.f ? 1.0f / l : 0.f;
+            if (sinks && m != -INFINITY) {
+                // a sink: one more term 2^sink (log2 units, not scaled) in the denominator.  l is a sum of terms
+                // relative to the base m, so with M = max(m, sink): 2^(m - M) / (l 2^(m - M) + 2^(sink - M))
+                const float sk = sinks[h] * 1.4426950408889634f, M = fmaxf(m, sk), a = exp2f(m - M);
+                inv = a / (l * a + exp2f(sk - M));
+            }
             bf16* dst = out + ((size_t)(tok0 + row) * nq + h) * HD;
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -406,7 +413,7 @@ extern "C" int vl_flash_tc5_head_dim() { return HD; }
 extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
                                     const int* block_table, int max_blocks, const int* tiles, int num_tiles,
                                     int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                                    unsigned* err, void* stream) {
+                                    unsigned* err, const float* sinks, void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || num_pages <= 0) return VL_ERR_ARGUMENT;
@@ -434,5 +441,5 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
     if (e != cudaSuccess) return (int)e;
     return vl_launch(flash_tc5_kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
                      map_k, map_v, pages_k, pages_v, use_pages, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
-                     num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
+                     num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks);
 }

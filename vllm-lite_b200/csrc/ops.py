@@ -46,14 +46,14 @@ _SIGNATURES = {
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("attention", "vl_decode_attention_merge"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                 c_int, c_int, c_void_p, c_void_p],
+                                                 c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode_fused"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -70,6 +70,9 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p],
     ("gemm_batched", "vl_gemm_batched_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p],
+    ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
+                                                c_void_p],
     ("moe", "vl_moe_route"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("moe", "vl_moe_align"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("moe", "vl_moe_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -361,18 +364,19 @@ def _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, h
 
 
 def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
-                  tile_rows=64):
+                  tile_rows=64, sinks=None):
     """Tensor-core (mma.sync) attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block
     table, index of the tile's first token in the step, tokens (<= tile_rows), position of the first
     token); the tiles of a step cover every token that the kernel is to serve once."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
+    _check_sinks(sinks, num_heads)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill: shapes disagree")
     _check(_fn("flash_attn", "vl_flash_prefill", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], int(tile_rows), num_heads, num_kv_heads, head_dim, k_cache.shape[2],
-        k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill")
+        k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _ptr(sinks), _stream()), "vl_flash_prefill")
     return out
 
 
@@ -386,11 +390,13 @@ def flash_tc5_supported(dtype, head_dim, page_size) -> bool:
             and (64 % page_size == 0 if page_size < 64 else page_size % 64 == 0))
 
 
-def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err):
+def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
+                      sinks=None):
     """Attention for prompt portions on the tcgen05 tensor cores; `tiles` as for `flash_prefill`,
     up to 128 tokens each."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
+    _check_sinks(sinks, num_heads)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill_tc5: shapes disagree")
     if not flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]):
@@ -398,7 +404,7 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
     _check(_fn("flash_tc5", "vl_flash_prefill_tc5", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill_tc5")
+        float(scale), int(window or 0), _ptr(err), _ptr(sinks), _stream()), "vl_flash_prefill_tc5")
     return out
 
 
@@ -433,7 +439,7 @@ def flash_decode_streams(dtype, num_tokens, num_kv_heads, head_dim, page_size, m
 
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
-                 stream_kernel=None, arrivals=None, fold=None):
+                 stream_kernel=None, arrivals=None, fold=None, sinks=None):
     """Tensor-core version of `decode_attention` (bfloat16): every block takes a chunk of a token's
     keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
     `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
@@ -448,6 +454,9 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     projection left them, every token is the last of its request, and the token's key and value are
     written to the cache by this launch (slots None: not written).  The same bits as the two kernels in turn."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
+    _check_sinks(sinks, num_heads)
+    if sinks is not None and fold is not None:
+        raise KernelError("flash_decode: the folded head work and sinks do not go together")
     _need(out, torch.bfloat16, "out", 2)
     _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
     _need(part_acc, torch.float32, "part_acc"); _need(part_ml, torch.float32, "part_ml")
@@ -478,7 +487,7 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
                 raise KernelError("flash_decode: too few arrival counters")
         if fold is None:
             _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
-                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _stream()), "vl_flash_decode")
+                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _ptr(sinks), _stream()), "vl_flash_decode")
         else:
             qw, kw, eps, inv_freq, rot, slots = fold
             for t, n in ((qw, "q_weight"), (kw, "k_weight"), (inv_freq, "inv_freq")):
@@ -502,7 +511,7 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
             return out
     _check(_fn("attention", "vl_decode_attention_merge")(
         _ptr(part_acc), _ptr(part_ml), _ptr(positions), _ptr(out), dtype_code(out.dtype), T, num_heads, head_dim,
-        chunk, S, int(window or 0), _ptr(token_index), _stream()), "vl_decode_attention_merge")
+        chunk, S, int(window or 0), _ptr(token_index), _ptr(sinks), _stream()), "vl_decode_attention_merge")
     return out
 
 
@@ -628,6 +637,38 @@ def gemm_grouped(rows, w, out, tile_group, bm):
     _check(_fn("gemm_batched", "vl_gemm_batched_nt")(
         _ptr(rows), _ptr(w), _ptr(out), dtype_code(rows.dtype), cap, N, K, K, K, N, 0, 0, 0, 1, _ptr(tile_group), N * K,
         int(bm), _stream()), "vl_gemm_batched_nt")
+    return out
+
+
+def gemm_grouped_fused_ok(dtype, K, N, act=None) -> bool:
+    """Whether `gemm_grouped_fused` takes a product of these sizes (bfloat16, rows on 16-byte boundaries;
+    with an activation, gate and up rows interleaved in blocks of 8, so N a multiple of 16)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = build.load("gemm_batched").vl_gemm_grouped_fused_ok
+    fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
+    return bool(fn(int(K), int(N), -1 if act is None else ACTIVATIONS[act]))
+
+
+def gemm_grouped_fused(a, w, out, tile_group, bm, row_index, index_div, row_scale=None, act=None, alpha=1.0, limit=0.0,
+                       shift=0.0):
+    """The grouped product with a routed feed-forward's neighbours folded in (bfloat16, tensor cores):
+    sorted row m is row row_index[m] // index_div of a [rows, K] (negative: zeros), times w[tile_group[y]]
+    ([G, N, K]); the float32 sums are multiplied by row_scale[row_index[m]] when given; with `act`, w holds
+    blocks of 8 gate rows and their 8 up rows and out is [cap, N / 2] = act(gate, up), else out is [cap, N]."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, torch.bfloat16, "out", 2)
+    _need(tile_group, torch.int32, "tile_group", 1); _need(row_index, torch.int32, "row_index", 1)
+    G, N, K = w.shape
+    cap = row_index.shape[0]
+    width = N // 2 if act is not None else N
+    if a.shape[1] != K or out.shape != (cap, width) or cap % bm or tile_group.shape[0] < cap // bm:
+        raise KernelError("gemm_grouped_fused: shapes disagree")
+    if row_scale is not None:
+        _need(row_scale, torch.float32, "row_scale")
+    _check(_fn("gemm_batched", "vl_gemm_grouped_fused")(
+        _ptr(a), _ptr(w), _ptr(out), cap, N, K, K, width, _ptr(tile_group), N * K, int(bm), _ptr(row_index), int(index_div),
+        _ptr(row_scale), -1 if act is None else ACTIVATIONS[act], float(alpha), float(limit), float(shift), _stream()),
+        "vl_gemm_grouped_fused")
     return out
 
 

@@ -36,7 +36,7 @@ def folds_head_work(dtype, step, spec, group, num_tokens) -> bool:
     return -(-int(group.max_context) // chunk) <= FOLD_MAX_CHUNKS
 
 
-def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None):
+def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None, sinks=None):
     chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context, head_dim=spec.head_dim)
     S, n_acc, n_ml = ops.decode_attention_scratch(num_tokens, spec.num_heads, spec.head_dim, max_context, chunk)
     part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
@@ -45,7 +45,7 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
     arrivals = step.workspace.zeros(step.tag + "attn.arrivals", ops.flash_decode_arrivals(num_tokens, spec.num_heads, spec.num_kv_heads),
                                     torch.int32)
     return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index,
-                            arrivals=arrivals, fold=fold)
+                            arrivals=arrivals, fold=fold, sinks=sinks)
 
 
 def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None):
@@ -54,26 +54,22 @@ def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None):
     head work that the mixer left undone.
     `sinks` (float32 [num_heads]): a number per head that joins every softmax denominator as exp(sink)."""
     from ..csrc import ops
-    if sinks is not None:
-        args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
-                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
-        return ops.paged_attention(*args, step.err, sinks=sinks)
     if fold is not None and not folds_head_work(qkv.dtype, step, spec, group, qkv.shape[0]):
         raise ValueError("this step's attention kernel does not fold the head norm and rotation in")
     args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
             spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
     if ops.flash_supported(qkv.dtype, spec.head_dim):
         if step.max_query_len == 1:
-            return _decode(ops, args, step, spec, group, qkv.shape[0], group.max_context, fold=fold)
+            return _decode(ops, args, step, spec, group, qkv.shape[0], group.max_context, fold=fold, sinks=sinks)
         if step.query_tiles is not None:
             tile_args = (qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
                          spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
             if step.max_query_len > 64 and ops.flash_tc5_supported(qkv.dtype, spec.head_dim, group.page_size):
-                ops.flash_prefill_tc5(*tile_args)
+                ops.flash_prefill_tc5(*tile_args, sinks=sinks)
             else:
-                ops.flash_prefill(*tile_args, tile_rows=QUERY_TILE)
+                ops.flash_prefill(*tile_args, tile_rows=QUERY_TILE, sinks=sinks)
             if step.single_tokens is not None:
                 _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
-                        token_index=step.single_tokens)
+                        token_index=step.single_tokens, sinks=sinks)
             return out
-    return ops.paged_attention(*args, step.err)
+    return ops.paged_attention(*args, step.err, sinks=sinks)

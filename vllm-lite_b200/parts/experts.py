@@ -12,6 +12,11 @@ of rows (every expert's rows padded to whole tiles), a gather kernel lays the (s
 order, two grouped products with the activation between them run over the tiles, each tile with its
 expert's matrices, and a last kernel sums a token's results in the order of its choices.  A row's
 arithmetic does not depend on where it was sorted to, so logits do not depend on the batch.
+
+In bfloat16 (sizes permitting) the first product does the work of its neighbours: it reads the tokens'
+rows through the sorted index (no sorted copy), applies the expert weight to its float32 sums
+(W (s h) = s (W h)) and the activation to its own tile (gate and up rows interleaved in blocks of 8), so
+the step is router, sort, two products and the sum: five launches instead of seven.
 """
 from __future__ import annotations
 
@@ -50,9 +55,16 @@ class RoutedExperts:
         names = [spec.expert_prefix.format(e) for e in range(E)]
         # the router works in float32 whatever the model's dtype (exact from bfloat16)
         self.router = weights[spec.router].to(device=ctx.device, dtype=torch.float32).contiguous()
-        # per expert [gate rows; up rows], stacked over experts: [E, 2I, H]; down: [E, H, I]
-        self.gate_up = torch.stack([torch.cat([weights[p + gate], weights[p + up]], dim=0) for p in names]).contiguous()
-        self.down = torch.stack([weights[p + down] for p in names]).contiguous()
+        I, H = spec.intermediate_size, spec.hidden_size
+        self.fused = I % 8 == 0 and ops.gemm_grouped_fused_ok(ctx.dtype, H, 2 * I, spec.activation)
+        if self.fused:
+            # per expert blocks of 8 gate rows followed by their 8 up rows: [E, 2I, H]
+            self.gate_up = torch.stack([torch.stack([weights[p + gate].view(I // 8, 8, H), weights[p + up].view(I // 8, 8, H)],
+                                                    dim=1).reshape(2 * I, H) for p in names]).contiguous()
+        else:
+            # per expert [gate rows; up rows], stacked over experts: [E, 2I, H]
+            self.gate_up = torch.stack([torch.cat([weights[p + gate], weights[p + up]], dim=0) for p in names]).contiguous()
+        self.down = torch.stack([weights[p + down] for p in names]).contiguous()          # [E, H, I]
 
     def __call__(self, h, step):
         from ..csrc import ops
@@ -68,9 +80,14 @@ class RoutedExperts:
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
         ops.moe_route(h, self.router, top, ids, weights, s.score, s.renormalize)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
-        rows = ops.moe_gather(h, sorted_rows, weights, top, ws.get(tag + "moe.rows", (cap, H), self.dtype), s.scale_input)
-        gu = ops.gemm_grouped(rows, self.gate_up, ws.get(tag + "moe.gate_up", (cap, 2 * I), self.dtype), tile_group, bm)
-        act = ops.gated_act(gu, ws.get(tag + "moe.act", (cap, I), self.dtype), s.activation, 0, s.alpha, s.limit, s.up_shift)
+        act = ws.get(tag + "moe.act", (cap, I), self.dtype)
+        if self.fused:
+            ops.gemm_grouped_fused(h, self.gate_up, act, tile_group, bm, sorted_rows, top,
+                                   weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
+        else:
+            rows = ops.moe_gather(h, sorted_rows, weights, top, ws.get(tag + "moe.rows", (cap, H), self.dtype), s.scale_input)
+            gu = ops.gemm_grouped(rows, self.gate_up, ws.get(tag + "moe.gate_up", (cap, 2 * I), self.dtype), tile_group, bm)
+            ops.gated_act(gu, act, s.activation, 0, s.alpha, s.limit, s.up_shift)
         res = ops.gemm_grouped(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, bm)
         out = ws.get(tag + "moe.out", (T, H), self.dtype)
         return ops.moe_combine(res, place, weights, top, out, not s.scale_input)
