@@ -416,6 +416,181 @@ def read_ceiling(cfg, batch, context):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------
+# --kikepel: the Kikepel decoder (latent attention with window and sink, routed experts, post-norm blocks)
+# beside the Qwen3 decoder at equal width, depth, heads and active feed-forward width
+# ---------------------------------------------------------------------------------------------------
+# name: (width, heads, dim, vdim, q_rank, kv_rank, window, dense ff, expert ff, experts, top, vocab)
+KIKEPEL_SIZES = {"2k": (2048, 16, 128, 128, 768, 128, 1024, 8192, 1024, 32, 4, 65536),
+                 "4k": (4096, 32, 128, 128, 1536, 128, 4096, 12288, 1408, 64, 6, 65536),
+                 "4k-r256": (4096, 32, 128, 128, 1536, 256, 4096, 12288, 1408, 64, 6, 65536)}
+# kernels of the new design and the like kernels of the closest model, by the name of their entry in csrc/ops.py
+TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_decode", "gemm_heads", "gemm_grouped",
+             "gemm_grouped_fused", "gemm_grouped_tc5", "gemm_bf16_small_m", "gemm_bf16_tc5", "gemm_bf16_tc5_pair", "layernorm_add",
+             "layernorm_rows", "add_rmsnorm", "latent_norm_write", "qk_norm_rope_write", "moe_route", "moe_align",
+             "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias")
+
+
+def kikepel_config(size, layers):
+    W, H, D, V, QR, KR, win, ff, eff, E, top, vocab = KIKEPEL_SIZES[size]
+    mix = dict(heads=H, dim=D, vdim=V, q_rank=QR, kv_rank=KR, scale=D ** -0.5, mask=dict(size=win))
+    moe = dict(kind="moe", expert=dict(ff=eff, limit=7.0), router=dict(experts=E, top=top))
+    kinds = [("latent_attention", dict(kind="dense", ff=ff)), ("latent_attention", moe), ("latent_attention_2", moe),
+             ("latent_attention", moe)]
+    return dict(architecture="Kikepel", vocab=vocab, width=W, norm=dict(eps=1e-6), logit_scale=1.0, logit_softcap=30.0,
+                max_position_embeddings=16384,
+                layers=[dict(type=kinds[i % 4][0], mixer=mix, mlp=kinds[i % 4][1]) for i in range(layers)])
+
+
+def timed_step(runner, entries):
+    """One step with every kernel of csrc/ops.py between two CUDA events.  The launches queue up behind a
+    kernel that only waits, so that the events see the kernels back to back and not the host's pace.
+    Returns {op: [launches, microseconds]} (library products through torch.mm are 'library_mm')."""
+    import torch
+    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.parts import matmul
+    records, saved = [], {}
+    def wrap(name, fn):
+        def inner(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            records.append((name, e0, e1))
+            return r
+        return inner
+    for name in TIMED_OPS:
+        saved[name] = getattr(ops, name)
+        setattr(ops, name, wrap(name, saved[name]))
+    mm = torch.mm
+    torch.mm = wrap("library_mm", mm)
+    graphs, runner.decode_graphs = runner.decode_graphs, False
+    try:
+        torch.cuda.synchronize()
+        torch.cuda._sleep(60_000_000)
+        runner.step(entries)
+        torch.cuda.synchronize()
+    finally:
+        for name, fn in saved.items():
+            setattr(ops, name, fn)
+        torch.mm = mm
+        runner.decode_graphs = graphs
+    out = {}
+    for name, e0, e1 in records:
+        rec = out.setdefault(name, [0, 0.0])
+        rec[0] += 1
+        rec[1] += e0.elapsed_time(e1) * 1e3
+    # the products count twice where an outer entry (gemm_bf16_tc5 ...) is itself an op: they are leaves here
+    return {k: [v[0], round(v[1], 1)] for k, v in sorted(out.items())}
+
+
+def kikepel_bench(args):
+    import torch
+    from vllm_lite_b200.engine import LLMEngine, StepEntry, random_model
+    size, layers = args.kikepel, args.layers or 8
+    W, H, D, V, QR, KR, win, ff, eff, E, top, vocab = KIKEPEL_SIZES[size]
+    context, pk = args.context, peaks()
+    warmup = max(args.warmup, 3)
+    qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=max(1, H // 4),
+                head_dim=128, intermediate_size=top * eff, vocab_size=vocab, max_position_embeddings=16384)
+    results = {}
+    for name, cfg in (("kikepel", kikepel_config(size, layers)), ("qwen3", qwen)):
+        _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        slack = 256
+        pages = 64 * (-(-(context + slack) // args.block_size) + 1) + PREFILL_TOKENS // args.block_size + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size,
+                           max_batch_size=64, max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
+                           max_model_len=context + slack)
+        del weights
+        runner, sampler = engine.runner, engine.sampler
+        for t in runner.storage.paged:
+            t.normal_()
+        res = {}
+        pms = prefill_run(runner, vocab)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tokens_per_s": round(PREFILL_TOKENS / pms * 1e3, 1)}
+        for b in (8, 64):
+            ms, launches, _ = decode_run(runner, sampler, b, context, warmup, args.steps, "random", vocab, f"d{b}.")
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b * 1e3 / ms, 1), "launches": round(launches)}
+        gen = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        res["kernels_prefill"] = timed_step(runner, [StepEntry("kp", prompt, [PREFILL_TOKENS - 1])])
+        runner.release("kp")
+        ids = [f"kd{i}" for i in range(64)]
+        for rid in ids:
+            runner.cache.admit(rid)
+            runner.cache.append(rid, context - 1)
+        res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+        for rid in ids:
+            runner.release(rid)
+        runner.check_device_errors()
+        res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
+        results[name] = res
+        del engine, runner, sampler
+        torch.cuda.empty_cache()
+    # ---- the new kernels against their rooflines, beside the like kernels of the closest model ---------
+    T, B = PREFILL_TOKENS, 64
+    keys = lambda w: sum(min(p + 1, w) for p in range(T))          # keys all queries of the prompt read
+    nsink = sum(1 for i in range(layers) if i % 4 != 2)
+    k, q = results["kikepel"], results["qwen3"]
+    def us(res, step, names):
+        return sum(res[step].get(n, [0, 0.0])[1] for n in names)
+    roof = {}
+    att = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_decode")
+    tf = lambda flops, micro: round(flops / (micro * 1e-6) / 1e12, 1) if micro else None
+    gb = lambda nbytes, micro: round(nbytes / (micro * 1e-6) / 1e9, 1) if micro else None
+    roof["attention_prefill_tflops"] = {
+        "kikepel": tf(layers * 4.0 * H * KR * keys(win), us(k, "kernels_prefill", att)),
+        "qwen3": tf(layers * 4.0 * H * 128 * keys(T), us(q, "kernels_prefill", att))}
+    roof["attention_decode_gbs"] = {
+        "kikepel": gb(layers * B * min(context, win) * KR * 2.0, us(k, "kernels_decode_b64", att)),
+        "qwen3": gb(layers * B * context * 2.0 * max(1, H // 4) * 128 * 2.0, us(q, "kernels_decode_b64", att))}
+    head_flops = layers * 2.0 * T * H * KR * (D + V)
+    roof["per_head_products_prefill_tflops"] = {"kikepel": tf(head_flops, us(k, "kernels_prefill", ("gemm_heads",)))}
+    roof["per_head_products_decode_gbs"] = {"kikepel": gb(layers * H * KR * (D + V) * 2.0, us(k, "kernels_decode_b64", ("gemm_heads",)))}
+    nmoe = sum(1 for i in range(layers) if i % 4 != 0)
+    q_layer = (H + 2 * max(1, H // 4)) * 128 * W + W * H * 128 + 3 * W * top * eff      # matrix elements of a Qwen3 layer
+    roof["expert_products_prefill_tflops"] = {
+        "kikepel": tf(nmoe * 2.0 * T * top * 3 * W * eff, us(k, "kernels_prefill", ("gemm_grouped", "gemm_grouped_fused", "gemm_grouped_tc5"))),
+        "qwen3 (all dense products of the layers)": tf(layers * 2.0 * T * q_layer,
+                                                       us(q, "kernels_prefill", ("gemm_bf16_tc5", "gemm_bf16_tc5_pair", "library_mm")))}
+    touched = min(E, B * top)
+    roof["expert_products_decode_gbs"] = {
+        "kikepel (experts that 64 tokens can reach)": gb(nmoe * touched * 3.0 * W * eff * 2, us(k, "kernels_decode_b64", ("gemm_grouped", "gemm_grouped_fused"))),
+        "qwen3 (all products)": gb(q["weights_GB"] * 1e9 - 2.0 * vocab * W * 2, us(q, "kernels_decode_b64", ("library_mm", "gemm_bf16_small_m")))}
+    roof["norm_prefill_gbs"] = {
+        "kikepel layernorm_add (y in, x in and out, cast out)": gb(k["kernels_prefill"].get("layernorm_add", [0])[0] * T * W * 12.0,
+                                                                  us(k, "kernels_prefill", ("layernorm_add",))),
+        "qwen3 add_rmsnorm (delta in, x in and out, h out)": gb(q["kernels_prefill"].get("add_rmsnorm", [0])[0] * T * W * 12.0,
+                                                               us(q, "kernels_prefill", ("add_rmsnorm",)))}
+    roof["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    print(json.dumps({"kikepel_bench": size, "layers": layers, "context": context, "steps": args.steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, uniform token ids)",
+                      "config": {"kikepel": dict(zip(("width", "heads", "dim", "vdim", "q_rank", "kv_rank", "window", "dense_ff",
+                                                      "expert_ff", "experts", "top", "vocab"), KIKEPEL_SIZES[size])),
+                                 "qwen3": {k_: qwen[k_] for k_ in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                                    "head_dim", "intermediate_size", "vocab_size")}},
+                      "results": results, "roofline": roof, "sinks_in": nsink}))
+    return 0
+
+
+def _tensors_of(model):
+    """Every device tensor that the parts of a model hold (weights as they are resident)."""
+    import torch
+    seen, out, stack = set(), [], [model]
+    while stack:
+        obj = stack.pop()
+        if id(obj) in seen:
+            continue
+        seen.add(id(obj))
+        if isinstance(obj, torch.Tensor):
+            out.append(obj)
+        elif isinstance(obj, (list, tuple)):
+            stack.extend(obj)
+        elif hasattr(obj, "__dict__") and type(obj).__module__.startswith("vllm_lite_b200"):
+            stack.extend(v for k_, v in vars(obj).items() if k_ not in ("plan", "ctx", "spec"))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -440,6 +615,10 @@ def main(argv=None):
                          "default for --size 32b); default otherwise: what the largest batch needs at --context")
     ap.add_argument("--read-ceiling", action="store_true",
                     help="instead of timing steps: every kernel of a decode step alone beside a kernel that only reads as many bytes")
+    ap.add_argument("--kikepel", default=None, choices=sorted(KIKEPEL_SIZES), metavar="SIZE",
+                    help="instead of the default workload: the Kikepel decoder at layer sizes " + ", ".join(sorted(KIKEPEL_SIZES))
+                         + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
+                           "and 64, and every kernel of a step between CUDA events (--layers, default 8; --context, --steps)")
     ap.add_argument("--check-fp32", action="store_true",
                     help="instead of timing: the model in true float32, whole prompt against cut prompt, bit for bit")
     args = ap.parse_args(argv)
@@ -450,6 +629,8 @@ def main(argv=None):
         return 2
     warmup = max(args.warmup, 3)
 
+    if args.kikepel:
+        return kikepel_bench(args)
     import torch
     from vllm_lite_b200.csrc import ops
     from vllm_lite_b200.engine import LLMEngine, random_model

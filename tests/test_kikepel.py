@@ -335,6 +335,9 @@ def test_gated_activations_and_capped_logits(dtype):
     close(ops().gated_act(gu, out, "capped_swish", 0, 1.702, lim, 1.0), gc * torch.sigmoid(1.702 * gc) * (uc + 1.0), dtype,
           "capped swish gate")
     close(ops().gated_act(gu, out, "silu"), g * torch.sigmoid(g) * u, dtype, "silu gate")
+    bias = rand((74,), 12)
+    close(ops().gated_act(gu, out, "relu", bias=bias), torch.relu(g + bias.double()[:37]) * (u + bias.double()[37:]), dtype,
+          "relu gate with the projections' biases")
     z = rand((4, 50), 10, torch.float32, 10.0)
     want = 6.0 * torch.tanh(z.double() * 1.7 / 6.0)
     close(ops().scale_softcap(z.clone(), 1.7, 6.0), want, torch.float32, "capped logits")
@@ -343,7 +346,8 @@ def test_gated_activations_and_capped_logits(dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,ff", [(1, 4, 1, 24), (9, 5, 2, 40), (150, 8, 3, 17), (33, 3, 3, 64)])
+@pytest.mark.parametrize("T,E,top,ff", [(1, 4, 1, 24), (9, 5, 2, 40), (150, 8, 3, 17), (33, 3, 3, 64), (600, 4, 2, 136),
+                                        (700, 8, 3, 40)])
 def test_routed_experts_part(dtype, T, E, top, ff):
     """The whole feed-forward part (router, sort, grouped products, activation, sum) against the plain loop
     over tokens; router weights are wide apart so that both sides choose the same experts."""
@@ -366,9 +370,15 @@ def test_routed_experts_part(dtype, T, E, top, ff):
     ids = step.workspace.get("moe.ids", (T, top), torch.int32).cpu()
     assert torch.equal(ids.long(), idx), "the router chose other experts"
     close(got, want, dtype, "routed experts")
-    # the same rows alone give the same bits: a row's arithmetic does not depend on its place among the sorted rows
+    # the same row alone: the same bits where both steps run on the same kernels (a row's arithmetic does not
+    # depend on its place among the sorted rows); steps of many rows take the tcgen05 products, whose sums
+    # are rounded alike but not added in the same order
     alone = part(h[T // 2:T // 2 + 1].contiguous(), step).clone()
-    assert torch.equal(alone[0], part(h, step)[T // 2])
+    again = part(h, step)[T // 2]
+    if T * top < 1024 or dtype == torch.float32:
+        assert torch.equal(alone[0], again)
+    else:
+        close(alone[0], again.double(), dtype, "a row alone against the row in a long step")
 
 
 def reference_attention(q, c, pos, window, scale, sinks):

@@ -41,14 +41,15 @@ extern "C" int vl_silu_mul(const void* gu, void* out, int dtype, int T, int I, i
 //   VL_ACT_SILU          silu(g) * u
 //   VL_ACT_RELU          max(g, 0) * u
 //   VL_ACT_CAPPED_SWISH  g' = min(g, limit), u' = clamp(u, -limit, limit):  g' * sigmoid(alpha * g') * (u' + shift)
-// alpha, limit and shift are the caller's constants (a limit <= 0 means no limit).
+// alpha, limit and shift are the caller's constants (a limit <= 0 means no limit).  `bias` (float32 [2I], optional)
+// is added to the gate and up columns first: the bias vectors of the two projections, which then need no pass of their own.
 #define VL_ACT_SILU 0
 #define VL_ACT_RELU 1
 #define VL_ACT_CAPPED_SWISH 2
 
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int group, int act,
-                                 float alpha, float limit, float shift) {
+                                 float alpha, float limit, float shift, const float* __restrict__ bias) {
     pdl_launch_dependents();
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -58,6 +59,10 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     const size_t gi = group > 0 ? (size_t)2 * group * (i / group) + i % group : (size_t)i;
     float g = to_f32(gu[t * 2 * (size_t)I + gi]);
     float u = to_f32(gu[t * 2 * (size_t)I + gi + (group > 0 ? group : I)]);
+    if (bias) {                                      // the projections' bias vectors, in the columns' own layout
+        g += bias[gi];
+        u += bias[gi + (group > 0 ? group : I)];
+    }
     float r;
     if (act == VL_ACT_RELU) {
         r = fmaxf(g, 0.f) * u;
@@ -71,7 +76,7 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 }
 
 extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, int group, int act, float alpha,
-                            float limit, float shift, void* stream) {
+                            float limit, float shift, const float* bias, void* stream) {
     if (T <= 0 || I <= 0) return VL_OK;
     if (group < 0 || (group > 0 && I % group) || act < 0 || act > 2) return VL_ERR_ARGUMENT;
     const size_t total = (size_t)T * I;
@@ -79,10 +84,10 @@ extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total, group,
-                         act, alpha, limit, shift);
+                         act, alpha, limit, shift, bias);
     if (dtype == VL_BF16)
         return vl_launch(gated_act_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, total, group,
-                         act, alpha, limit, shift);
+                         act, alpha, limit, shift, bias);
     return VL_ERR_UNSUPPORTED;
 }
 

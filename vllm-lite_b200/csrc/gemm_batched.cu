@@ -22,9 +22,9 @@ static inline bool vl_batched_simt_only() {
 #define GB_BN 64
 #define GB_BK 16
 
-template <typename T, int BM>
+template <typename T, typename TW, typename TC, int BM>
 __global__ void __launch_bounds__(256)
-gemm_batched_nt_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __restrict__ C, int M, int N, int K,
+gemm_batched_nt_kernel(const T* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
                        int lda, int ldw, int ldc, long long a_bs, long long w_bs, long long c_bs,
                        const int* __restrict__ tile_group, long long w_gs) {
     constexpr int TM = BM / 16;
@@ -36,8 +36,8 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __re
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * GB_BN;
     const T* Ab = A + (size_t)blockIdx.z * a_bs;
-    const T* Wb = W + (size_t)blockIdx.z * w_bs;
-    T* Cb = C + (size_t)blockIdx.z * c_bs;
+    const TW* Wb = W + (size_t)blockIdx.z * w_bs;
+    TC* Cb = C + (size_t)blockIdx.z * c_bs;
     if (tile_group) {
         const int g = tile_group[blockIdx.y];
         if (g < 0) return;
@@ -84,7 +84,7 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __re
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) Cb[(size_t)m * ldc + n] = from_f32<T>(acc[i][j]);
+            if (n < N) Cb[(size_t)m * ldc + n] = from_f32<TC>(acc[i][j]);
         }
     }
 }
@@ -135,9 +135,9 @@ __device__ __forceinline__ float gm_gated(float g, float u, int act, float alpha
     return g / (1.0f + expf(-g)) * u;
 }
 
-template <int BM>
+template <int BM, typename TC>
 __global__ void __launch_bounds__(128)
-gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* __restrict__ C, int M, int N, int K,
+gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
                              int lda, int ldw, int ldc, long long a_bs, long long w_bs, long long c_bs,
                              const int* __restrict__ tile_group, long long w_gs,
                              const int* __restrict__ row_index, int index_div, const float* __restrict__ row_scale,
@@ -153,7 +153,7 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * GM_BN;
     const bf16* Ab = A + (size_t)blockIdx.z * a_bs;
     const bf16* Wb = W + (size_t)blockIdx.z * w_bs;
-    bf16* Cb = C + (size_t)blockIdx.z * c_bs;
+    TC* Cb = C + (size_t)blockIdx.z * c_bs;
     if (tile_group) {
         const int g = tile_group[blockIdx.y];
         if (g < 0) return;
@@ -226,14 +226,14 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
             const int p = row_index ? row_index[m] : m;
             scale = p >= 0 ? row_scale[p] : 0.f;
         }
-        bf16* crow = Cb + (size_t)m * ldc;
+        TC* crow = Cb + (size_t)m * ldc;
         if (act == GM_ACT_NONE) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int n = n0 + wn * WN + nt * 8 + t2;
                 const float v0 = acc[nt][2 * half] * scale, v1 = acc[nt][2 * half + 1] * scale;
-                if (n < N) crow[n] = __float2bfloat16(v0);
-                if (n + 1 < N) crow[n + 1] = __float2bfloat16(v1);
+                if (n < N) crow[n] = from_f32<TC>(v0);
+                if (n + 1 < N) crow[n + 1] = from_f32<TC>(v1);
             }
         } else {
             // n-tiles come in pairs: 8 gate columns, then their 8 up columns; the pair writes 8 columns
@@ -243,7 +243,7 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const float gate = acc[2 * np][2 * half + e] * scale, up = acc[2 * np + 1][2 * half + e] * scale;
-                    if (n + e < N / 2) crow[n + e] = __float2bfloat16(gm_gated(gate, up, act, alpha, limit, shift));
+                    if (n + e < N / 2) crow[n + e] = from_f32<TC>(gm_gated(gate, up, act, alpha, limit, shift));
                 }
             }
         }
@@ -261,9 +261,9 @@ static int launch_batched_mma(const bf16* A, const bf16* W, bf16* C, int M, int 
     dim3 grid((N + GM_BN - 1) / GM_BN, (M + bm - 1) / bm, batch);
     if (grid.y > 65535 || grid.z > 65535) return VL_ERR_UNSUPPORTED;
     if (bm == 64)
-        return vl_launch(gemm_batched_bf16_mma_kernel<64>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
+        return vl_launch(gemm_batched_bf16_mma_kernel<64, bf16>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
                          c_bs, tile_group, w_gs, row_index, index_div, row_scale, act, alpha, limit, shift);
-    return vl_launch(gemm_batched_bf16_mma_kernel<16>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
+    return vl_launch(gemm_batched_bf16_mma_kernel<16, bf16>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
                      c_bs, tile_group, w_gs, row_index, index_div, row_scale, act, alpha, limit, shift);
 }
 
@@ -274,9 +274,9 @@ static int launch_batched(const T* A, const T* W, T* C, int M, int N, int K, int
     dim3 grid((N + GB_BN - 1) / GB_BN, (M + bm - 1) / bm, batch);
     if (grid.y > 65535 || grid.z > 65535) return VL_ERR_UNSUPPORTED;
     if (bm == 64)
-        return vl_launch(gemm_batched_nt_kernel<T, 64>, grid, dim3(256), 0, s, A, W, C, M, N, K, lda, ldw, ldc,
+        return vl_launch(gemm_batched_nt_kernel<T, T, T, 64>, grid, dim3(256), 0, s, A, W, C, M, N, K, lda, ldw, ldc,
                          a_bs, w_bs, c_bs, tile_group, w_gs);
-    return vl_launch(gemm_batched_nt_kernel<T, 16>, grid, dim3(256), 0, s, A, W, C, M, N, K, lda, ldw, ldc,
+    return vl_launch(gemm_batched_nt_kernel<T, T, T, 16>, grid, dim3(256), 0, s, A, W, C, M, N, K, lda, ldw, ldc,
                      a_bs, w_bs, c_bs, tile_group, w_gs);
 }
 
@@ -298,6 +298,36 @@ extern "C" int vl_gemm_batched_nt(const void* A, const void* W, void* C, int dty
         return launch_batched<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc,
                                     a_bs, w_bs, c_bs, batch, tile_group, w_gs, bm, s);
     }
+    return VL_ERR_UNSUPPORTED;
+}
+
+// z[M, N] = a[M, K] * w[N, K]^T with a in the activation dtype, w and z float32 (a router's logits: few
+// columns, float32 whatever the model's dtype).  Same kernel, same fixed order over K.
+extern "C" int vl_gemm_rows_f32w(const void* A, int a_dtype, const void* W, int w_dtype, float* C, int M, int N, int K,
+                                 void* stream) {
+    if (M <= 0 || N <= 0) return VL_OK;
+    if (K <= 0) return VL_ERR_ARGUMENT;
+    const int bm = M <= 16 ? 16 : 64;
+    dim3 grid((N + GB_BN - 1) / GB_BN, (M + bm - 1) / bm, 1);
+    if (grid.y > 65535) return VL_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (a_dtype == VL_BF16 && w_dtype == VL_BF16 && gm_aligned(A, W, K, K, K, 0, 0, 0) && !vl_batched_simt_only()) {
+        // both operands bfloat16: their products are exact in float32, the tensor cores add them in float32
+        if (bm == 64)
+            return vl_launch(gemm_batched_bf16_mma_kernel<64, float>, grid, dim3(128), 0, s, (const bf16*)A, (const bf16*)W, C, M, N,
+                             K, K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll, (const int*)nullptr, 1, (const float*)nullptr,
+                             GM_ACT_NONE, 0.f, 0.f, 0.f);
+        return vl_launch(gemm_batched_bf16_mma_kernel<16, float>, grid, dim3(128), 0, s, (const bf16*)A, (const bf16*)W, C, M, N, K,
+                         K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll, (const int*)nullptr, 1, (const float*)nullptr,
+                         GM_ACT_NONE, 0.f, 0.f, 0.f);
+    }
+#define ROWS_CASE(TA, TWV, BMV)                                                                                     \
+    return vl_launch(gemm_batched_nt_kernel<TA, TWV, float, BMV>, grid, dim3(256), 0, s, (const TA*)A, (const TWV*)W, C, M, N, \
+                     K, K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll)
+    if (a_dtype == VL_F32 && w_dtype == VL_F32) { if (bm == 64) ROWS_CASE(float, float, 64); ROWS_CASE(float, float, 16); }
+    if (a_dtype == VL_BF16 && w_dtype == VL_F32) { if (bm == 64) ROWS_CASE(bf16, float, 64); ROWS_CASE(bf16, float, 16); }
+    if (a_dtype == VL_BF16 && w_dtype == VL_BF16) { if (bm == 64) ROWS_CASE(bf16, bf16, 64); ROWS_CASE(bf16, bf16, 16); }
+#undef ROWS_CASE
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -2,9 +2,10 @@
 // experts' results back together.  The products themselves are the grouped form of
 // gemm_batched.cu, the experts' activation is in activation.cu.
 //
-//   vl_moe_route    z = W_r h (float32), score = sigmoid(z) or softmax(z); the `top` largest scores
-//                   pick the experts of a token (ties: the lower index), weights = the scores as they
-//                   are or divided by their sum.  -> expert ids [T, top], weights float32 [T, top]
+//   vl_moe_route    from the logits z = W_r h (float32, a product of csrc/gemm_batched.cu): score =
+//                   sigmoid(z) or softmax(z); the `top` largest pick the experts of a token (ties: the
+//                   lower index), weights = the scores as they are or divided by their sum.
+//                   -> expert ids [T, top], weights float32 [T, top]
 //   vl_moe_align    sorts the T * top (token, choice) pairs by expert into tiles of `bm` rows, every
 //                   expert's rows padded up to whole tiles: sorted_rows[r] = pair or -1,
 //                   tile_group[y] = expert of tile y or -1, place[pair] = r.  One block; where a pair
@@ -22,10 +23,9 @@
 #define MOE_SCORE_SOFTMAX 1
 #define MOE_MAX_EXPERTS 1024
 
-// one warp per token
-template <typename T>
+// one warp per token; z [ntok, E]: the router's logits (csrc/gemm_batched.cu: vl_gemm_rows_f32w)
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, int ntok, int E, int K, int top,
+moe_route_kernel(const float* __restrict__ z, int ntok, int E, int top,
                  int score_fn, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float s_scores[];                  // [4][E]
     pdl_launch_dependents();
@@ -34,14 +34,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, int ntok
     const int t = blockIdx.x * 4 + warp;
     if (t >= ntok) return;
     float* sc = s_scores + (size_t)warp * E;
-    const T* row = h + (size_t)t * K;
-    for (int e = 0; e < E; ++e) {
-        const float* w = wr + (size_t)e * K;
-        float acc = 0.f;
-        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(row[k]), w[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) sc[e] = acc;
-    }
+    for (int e = lane; e < E; e += 32) sc[e] = z[(size_t)t * E + e];
     __syncwarp();
     // The choice is made on the logits: both score functions grow with z, and a sigmoid that has
     // rounded to 1 for several experts would hide which of them is the largest.
@@ -153,21 +146,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
     }
 }
 
-extern "C" int vl_moe_route(const void* h, int dtype, const float* wr, int T, int E, int K, int top,
-                            int score_fn, int renorm, int* ids, float* weights, void* stream) {
+extern "C" int vl_moe_route(const float* z, int T, int E, int top, int score_fn, int renorm, int* ids, float* weights,
+                            void* stream) {
     if (T <= 0) return VL_OK;
-    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || K <= 0) return VL_ERR_ARGUMENT;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E) return VL_ERR_ARGUMENT;
     if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
-    cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)4 * E * sizeof(float);
-    const dim3 grid((T + 3) / 4);
-    if (dtype == VL_F32)
-        return vl_launch(moe_route_kernel<float>, grid, dim3(128), smem, s, (const float*)h, wr, T, E, K, top, score_fn,
-                         renorm, ids, weights);
-    if (dtype == VL_BF16)
-        return vl_launch(moe_route_kernel<bf16>, grid, dim3(128), smem, s, (const bf16*)h, wr, T, E, K, top, score_fn,
-                         renorm, ids, weights);
-    return VL_ERR_UNSUPPORTED;
+    return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream,
+                     z, T, E, top, score_fn, renorm, ids, weights);
 }
 
 // cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)

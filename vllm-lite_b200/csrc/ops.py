@@ -62,7 +62,8 @@ _SIGNATURES = {
                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    ("activation", "vl_gated_act"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    ("activation", "vl_gated_act"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p,
+                                     c_void_p],
     ("activation", "vl_scale_softcap"): [c_void_p, c_longlong, c_float, c_float, c_void_p],
     ("embed_norm", "vl_layernorm_add"): [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("embed_norm", "vl_layernorm_rows"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -73,7 +74,10 @@ _SIGNATURES = {
     ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                                 c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
                                                 c_void_p],
-    ("moe", "vl_moe_route"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                       c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
     ("moe", "vl_moe_align"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("moe", "vl_moe_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ("moe", "vl_moe_combine"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -534,18 +538,22 @@ def silu_mul(gate_up, out, group=0):
 ACTIVATIONS = {"silu": 0, "relu": 1, "capped_swish": 2}
 
 
-def gated_act(gate_up, out, act, group=0, alpha=1.0, limit=0.0, shift=0.0):
+def gated_act(gate_up, out, act, group=0, alpha=1.0, limit=0.0, shift=0.0, bias=None):
     """out[t, i] = f(gate_i, up_i) of gate_up [T, 2I] in the layouts of `silu_mul`.  act: "silu" (silu(g) u),
     "relu" (max(g, 0) u) or "capped_swish" (g' = min(g, limit), u' = clamp(u, -limit, limit):
-    g' sigmoid(alpha g') (u' + shift); limit <= 0: none)."""
+    g' sigmoid(alpha g') (u' + shift); limit <= 0: none).  `bias` (float32 [2I]) is added to gate_up first."""
     _need(gate_up, None, "gate_up", 2); _need(out, gate_up.dtype, "out", 2)
     T, I2 = gate_up.shape
     if I2 % 2 or out.shape != (T, I2 // 2):
         raise KernelError("gated_act: out must be [T, I] for gate_up [T, 2I]")
     if act not in ACTIVATIONS:
         raise KernelError(f"gated_act: unknown activation {act!r}; known: {', '.join(ACTIVATIONS)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+        if bias.shape[0] != I2:
+            raise KernelError("gated_act: the bias has one entry per column of gate_up")
     _check(_fn("activation", "vl_gated_act")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, int(group),
-                                             ACTIVATIONS[act], float(alpha), float(limit), float(shift), _stream()),
+                                             ACTIVATIONS[act], float(alpha), float(limit), float(shift), _ptr(bias), _stream()),
            "vl_gated_act")
     return out
 
@@ -682,17 +690,50 @@ def moe_sorted_rows(npairs, num_experts, bm) -> int:
     return -(-need // bm) * bm
 
 
-def moe_route(h, router, top, ids, weights, score="sigmoid", renormalize=False):
-    """h [T, K], router float32 [E, K]: ids int32 [T, top] = the experts with the largest scores,
-    weights float32 [T, top] = their scores (divided by their sum when `renormalize`)."""
-    _need(h, None, "h", 2); _need(router, torch.float32, "router", 2)
+def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False):
+    """h [T, K], router [E, K] (float32; or bfloat16 as stored, beside bfloat16 rows: products of two bfloat16 numbers
+    are exact in float32, so the tensor cores' float32 sums are the 32-bit logits of the rounded rows):
+    logits float32 [T, E] = h router^T; ids int32 [T, top] = the experts with
+    the largest logits, weights float32 [T, top] = their scores (divided by their sum when `renormalize`)."""
+    _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 2)
+    if router.dtype != torch.float32 and router.dtype != h.dtype:
+        raise KernelError("moe_route: the router is float32, or bfloat16 beside bfloat16 rows")
     _need(ids, torch.int32, "ids", 2); _need(weights, torch.float32, "weights", 2)
     T, K = h.shape
     E = router.shape[0]
-    if router.shape[1] != K or ids.shape != (T, top) or weights.shape != (T, top):
+    if router.shape[1] != K or ids.shape != (T, top) or weights.shape != (T, top) or logits.shape != (T, E):
         raise KernelError("moe_route: shapes disagree")
-    _check(_fn("moe", "vl_moe_route")(_ptr(h), dtype_code(h.dtype), _ptr(router), T, E, K, int(top), ROUTER_SCORES[score],
-                                      int(bool(renormalize)), _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
+    _check(_fn("gemm_batched", "vl_gemm_rows_f32w")(_ptr(h), dtype_code(h.dtype), _ptr(router), dtype_code(router.dtype),
+                                                    _ptr(logits), T, E, K, _stream()), "vl_gemm_rows_f32w")
+    _check(_fn("moe", "vl_moe_route")(_ptr(logits), T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)), _ptr(ids),
+                                      _ptr(weights), _stream()), "vl_moe_route")
+
+
+TC5_GROUPED_TILE = 128    # rows per tile of the grouped tcgen05 product
+
+
+def gemm_grouped_tc5_ok(dtype, pairs, num_experts, K) -> bool:
+    """Whether a routed feed-forward of `pairs` (token, choice) rows runs its products on the tcgen05 tensor cores:
+    bfloat16, rows on 16-byte boundaries, and enough rows that the experts' tiles of 128 rows are mostly full."""
+    return dtype == torch.bfloat16 and K % 8 == 0 and pairs >= max(1024, 96 * num_experts)
+
+
+def gemm_grouped_tc5(rows, w, out, tile_group, err, row_index=None, row_scale=None, act=None, alpha=1.0, limit=0.0, shift=0.0):
+    """The grouped product on the tcgen05 tensor cores: rows [cap, K] sorted in tiles of 128, w [G, N, K], out [cap, N]
+    or, with `act` (w then interleaves 8 gate rows with their 8 up rows), [cap, N / 2] = act(gate, up).
+    row_scale: the float32 sums of row m are multiplied by row_scale[row_index[m]] first."""
+    _need(rows, torch.bfloat16, "rows", 2); _need(w, torch.bfloat16, "w", 3); _need(out, torch.bfloat16, "out", 2)
+    _need(tile_group, torch.int32, "tile_group", 1)
+    G, N, K = w.shape
+    cap = rows.shape[0]
+    if rows.shape[1] != K or out.shape != (cap, N // 2 if act is not None else N) or cap % TC5_GROUPED_TILE \
+            or tile_group.shape[0] < cap // TC5_GROUPED_TILE:
+        raise KernelError("gemm_grouped_tc5: shapes disagree")
+    _check(_fn("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped")(
+        _ptr(rows), _ptr(w), _ptr(out), cap, N, K, G, _ptr(tile_group), _ptr(row_index), _ptr(row_scale),
+        -1 if act is None else ACTIVATIONS[act], float(alpha), float(limit), float(shift), _ptr(err), _stream()),
+        "vl_gemm_bf16_tc5_grouped")
+    return out
 
 
 def moe_align(ids, num_experts, bm, sorted_rows, tile_group, place):

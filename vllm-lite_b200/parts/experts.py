@@ -53,8 +53,12 @@ class RoutedExperts:
         gate, up, down = spec.names
         E = spec.num_experts
         names = [spec.expert_prefix.format(e) for e in range(E)]
-        # the router works in float32 whatever the model's dtype (exact from bfloat16)
-        self.router = weights[spec.router].to(device=ctx.device, dtype=torch.float32).contiguous()
+        # The router's logits are float32 sums whatever the model's dtype.  A router stored in bfloat16 beside
+        # bfloat16 rows stays as it is: the products of two bfloat16 numbers are exact in float32, so the tensor
+        # cores add the same numbers as a float32 product of the widened matrix would.
+        r = weights[spec.router]
+        keep = r.dtype == torch.bfloat16 and ctx.dtype == torch.bfloat16 and spec.hidden_size % 8 == 0
+        self.router = r.contiguous() if keep else r.to(device=ctx.device, dtype=torch.float32).contiguous()
         I, H = spec.intermediate_size, spec.hidden_size
         self.fused = I % 8 == 0 and ops.gemm_grouped_fused_ok(ctx.dtype, H, 2 * I, spec.activation)
         if self.fused:
@@ -71,16 +75,25 @@ class RoutedExperts:
         s, ws, tag = self.spec, step.workspace, step.tag
         T, E, top, I, H = h.shape[0], s.num_experts, s.top, s.intermediate_size, s.hidden_size
         pairs = T * top
-        bm = 16 if pairs <= SMALL_STEP_PAIRS else 64
+        big = self.fused and ops.gemm_grouped_tc5_ok(self.dtype, pairs, E, H) and I % 8 == 0
+        bm = ops.TC5_GROUPED_TILE if big else (16 if pairs <= SMALL_STEP_PAIRS else 64)
         cap = ops.moe_sorted_rows(pairs, E, bm)
         ids = ws.get(tag + "moe.ids", (T, top), torch.int32)
         weights = ws.get(tag + "moe.weights", (T, top), torch.float32)
         sorted_rows = ws.get(tag + "moe.sorted", (cap,), torch.int32)
         tile_group = ws.get(tag + "moe.tiles", (cap // bm,), torch.int32)
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
-        ops.moe_route(h, self.router, top, ids, weights, s.score, s.renormalize)
+        logits = ws.get(tag + "moe.logits", (T, E), torch.float32)
+        ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
         act = ws.get(tag + "moe.act", (cap, I), self.dtype)
+        if big:
+            # many rows: both products on the tcgen05 tensor cores, from a sorted copy of the tokens' rows
+            rows = ops.moe_gather(h, sorted_rows, weights, top, ws.get(tag + "moe.rows", (cap, H), self.dtype), False)
+            ops.gemm_grouped_tc5(rows, self.gate_up, act, tile_group, step.err, sorted_rows,
+                                 weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
+            res = ops.gemm_grouped_tc5(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, step.err)
+            return ops.moe_combine(res, place, weights, top, ws.get(tag + "moe.out", (T, H), self.dtype), not s.scale_input)
         if self.fused:
             ops.gemm_grouped_fused(h, self.gate_up, act, tile_group, bm, sorted_rows, top,
                                    weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)

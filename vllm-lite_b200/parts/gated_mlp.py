@@ -2,7 +2,8 @@
 down(act(gate(h) + b_g) * (up(h) + b_u)) + b_d, act = "silu" or "relu".
 
 gate and up are stacked into one matrix (gate rows, then up rows) so that one product serves both;
-the biases are added in float32 by the linear layer, the activation is one kernel on the stacked result.
+the activation is one kernel on the stacked result and adds the two projections' biases on the way (float32);
+the down projection's bias is added by the linear layer.
 The SwiGLU part (`parts/mlp.py`) is the bias-free special case whose activation the product kernels
 fuse; this part serves what that one does not take."""
 from __future__ import annotations
@@ -37,13 +38,15 @@ class GatedMlp:
         self.dtype = ctx.dtype
         gate, up, down = spec.names
         b = spec.bias_suffix
-        bias = torch.cat([weights[gate + b].float(), weights[up + b].float()], dim=0) if spec.bias else None
-        self.gate_up = Linear(torch.cat([weights[gate], weights[up]], dim=0).contiguous(), bias)
+        self.gate_up_bias = None
+        if spec.bias:
+            self.gate_up_bias = torch.cat([weights[gate + b].float(), weights[up + b].float()], dim=0).contiguous()
+        self.gate_up = Linear(torch.cat([weights[gate], weights[up]], dim=0).contiguous())
         self.down = Linear(weights[down], weights[down + b].float() if spec.bias else None)
 
     def __call__(self, h, step):
         from ..csrc import ops
         gu = self.gate_up(h, step, "mlp.gate_up")
         act = step.workspace.get(step.tag + "mlp.act", (gu.shape[0], self.spec.intermediate_size), gu.dtype)
-        ops.gated_act(gu, act, self.spec.activation)
+        ops.gated_act(gu, act, self.spec.activation, bias=self.gate_up_bias)
         return self.down(act, step, "mlp.down")
