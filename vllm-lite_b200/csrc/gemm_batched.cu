@@ -92,7 +92,7 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const TW* __restrict__ W, TC* __
 // ---------------------------------------------------------------------------------------------------
 // The same products on the tensor cores (bfloat16, mma.sync m16n8k16, float32 accumulation): tiles of
 // BM x 64 x 32 (BM = 64: four warps of 16 rows; BM = 16: four warps of 16 columns), operands brought by
-// 16-byte cp.async through a ring of three stages into padded rows, fragments by ldmatrix.  Taken when
+// 16-byte cp.async through a ring of four stages of 64 columns of K into padded rows, fragments by ldmatrix.  Taken when
 // every row of A and W starts on a 16-byte boundary (K, the strides and the batch offsets multiples of 8).
 // Three things a routed feed-forward folds into its first product:
 //   row_index  row m of A is row row_index[m] / index_div of the matrix A points to (negative: a row of
@@ -104,9 +104,9 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const TW* __restrict__ W, TC* __
 // Every output element is summed over K in steps of 16 in order, whatever its place in the tile.
 // ---------------------------------------------------------------------------------------------------
 #define GM_BN 64
-#define GM_BK 32
-#define GM_LDS 40
-#define GM_NST 3
+#define GM_BK 64
+#define GM_LDS 72
+#define GM_NST 4
 #define GM_ACT_NONE (-1)
 
 __device__ __forceinline__ void gm_cp_async16(void* smem, const void* gmem, bool valid) {
@@ -143,8 +143,10 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
                              const int* __restrict__ row_index, int index_div, const float* __restrict__ row_scale,
                              int act, float alpha, float limit, float shift) {
     constexpr int WARPS_M = BM / 16, WARPS_N = 4 / WARPS_M, WN = GM_BN / WARPS_N, NT = WN / 8;
-    __shared__ __align__(16) bf16 As[GM_NST][BM][GM_LDS];
-    __shared__ __align__(16) bf16 Ws[GM_NST][GM_BN][GM_LDS];
+    // the ring is larger than the 48 KB a kernel may declare: dynamic shared memory
+    extern __shared__ __align__(16) unsigned char gm_smem[];
+    bf16 (*As)[BM][GM_LDS] = reinterpret_cast<bf16 (*)[BM][GM_LDS]>(gm_smem);
+    bf16 (*Ws)[GM_BN][GM_LDS] = reinterpret_cast<bf16 (*)[GM_BN][GM_LDS]>(gm_smem + (size_t)GM_NST * BM * GM_LDS * sizeof(bf16));
     __shared__ int s_src[BM];                                    // source row of every row of the tile (-1: zeros)
     pdl_launch_dependents();
     pdl_wait();
@@ -177,16 +179,17 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
     const int KT = (K + GM_BK - 1) / GM_BK;
     auto load_stage = [&](int st, int kt) {
         const int k0 = kt * GM_BK;
-        for (int idx = tid; idx < BM * 4; idx += 128) {
-            const int r = idx >> 2, k = k0 + (idx & 3) * 8;
+        constexpr int CH = GM_BK / 8;                           // 16-byte pieces of a row of the stage
+        for (int idx = tid; idx < BM * CH; idx += 128) {
+            const int r = idx / CH, c = idx % CH, k = k0 + c * 8;
             const int src = s_src[r];
             const bool ok = src >= 0 && k < K;
-            gm_cp_async16(&As[st][r][(idx & 3) * 8], ok ? Ab + (size_t)src * lda + k : Ab, ok);
+            gm_cp_async16(&As[st][r][c * 8], ok ? Ab + (size_t)src * lda + k : Ab, ok);
         }
-        for (int idx = tid; idx < GM_BN * 4; idx += 128) {
-            const int r = idx >> 2, k = k0 + (idx & 3) * 8;
+        for (int idx = tid; idx < GM_BN * CH; idx += 128) {
+            const int r = idx / CH, c = idx % CH, k = k0 + c * 8;
             const bool ok = n0 + r < N && k < K;
-            gm_cp_async16(&Ws[st][r][(idx & 3) * 8], ok ? Wb + (size_t)(n0 + r) * ldw + k : Wb, ok);
+            gm_cp_async16(&Ws[st][r][c * 8], ok ? Wb + (size_t)(n0 + r) * ldw + k : Wb, ok);
         }
     };
 #pragma unroll
@@ -250,6 +253,19 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
     }
 }
 
+template <int BM, typename TC, typename... Args>
+static int launch_mma_kernel(dim3 grid, cudaStream_t s, Args... args) {
+    const size_t smem = (size_t)GM_NST * (BM + GM_BN) * GM_LDS * sizeof(bf16);
+    auto kern = gemm_batched_bf16_mma_kernel<BM, TC>;
+    static bool ready = false;                               // per instantiation
+    if (!ready) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        ready = true;
+    }
+    return vl_launch(kern, grid, dim3(128), smem, s, args...);
+}
+
 static bool gm_aligned(const void* A, const void* W, int K, int lda, int ldw, long long a_bs, long long w_bs, long long w_gs) {
     return !(K % 8 || lda % 8 || ldw % 8 || a_bs % 8 || w_bs % 8 || w_gs % 8 || (((uintptr_t)A | (uintptr_t)W) & 15));
 }
@@ -261,10 +277,10 @@ static int launch_batched_mma(const bf16* A, const bf16* W, bf16* C, int M, int 
     dim3 grid((N + GM_BN - 1) / GM_BN, (M + bm - 1) / bm, batch);
     if (grid.y > 65535 || grid.z > 65535) return VL_ERR_UNSUPPORTED;
     if (bm == 64)
-        return vl_launch(gemm_batched_bf16_mma_kernel<64, bf16>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
-                         c_bs, tile_group, w_gs, row_index, index_div, row_scale, act, alpha, limit, shift);
-    return vl_launch(gemm_batched_bf16_mma_kernel<16, bf16>, grid, dim3(128), 0, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs,
-                     c_bs, tile_group, w_gs, row_index, index_div, row_scale, act, alpha, limit, shift);
+        return launch_mma_kernel<64, bf16>(grid, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
+                                           row_index, index_div, row_scale, act, alpha, limit, shift);
+    return launch_mma_kernel<16, bf16>(grid, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
+                                       row_index, index_div, row_scale, act, alpha, limit, shift);
 }
 
 template <typename T>
@@ -304,29 +320,29 @@ extern "C" int vl_gemm_batched_nt(const void* A, const void* W, void* C, int dty
 // z[M, N] = a[M, K] * w[N, K]^T with a in the activation dtype, w and z float32 (a router's logits: few
 // columns, float32 whatever the model's dtype).  Same kernel, same fixed order over K.
 extern "C" int vl_gemm_rows_f32w(const void* A, int a_dtype, const void* W, int w_dtype, float* C, int M, int N, int K,
-                                 void* stream) {
+                                 int slices, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
-    if (K <= 0) return VL_ERR_ARGUMENT;
-    const int bm = M <= 16 ? 16 : 64;
-    dim3 grid((N + GB_BN - 1) / GB_BN, (M + bm - 1) / bm, 1);
+    if (K <= 0 || slices <= 0 || K % slices) return VL_ERR_ARGUMENT;
+    // slices: K is cut into that many equal parts, each a "batch" of the launch that reads its columns of A
+    // and W and writes its own [M, N] sums to C + slice * M * N (the reader adds them in order)
+    const int Kc = K / slices;
+    const long long cs = (long long)M * N;
+    const int bm = 16;                                    // few columns: short tiles give the launch its blocks
+    dim3 grid((N + GB_BN - 1) / GB_BN, (M + bm - 1) / bm, slices);
     if (grid.y > 65535) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (a_dtype == VL_BF16 && w_dtype == VL_BF16 && gm_aligned(A, W, K, K, K, 0, 0, 0) && !vl_batched_simt_only()) {
+    if (a_dtype == VL_BF16 && w_dtype == VL_BF16 && gm_aligned(A, W, Kc, K, K, Kc, Kc, 0) && !vl_batched_simt_only()) {
         // both operands bfloat16: their products are exact in float32, the tensor cores add them in float32
-        if (bm == 64)
-            return vl_launch(gemm_batched_bf16_mma_kernel<64, float>, grid, dim3(128), 0, s, (const bf16*)A, (const bf16*)W, C, M, N,
-                             K, K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll, (const int*)nullptr, 1, (const float*)nullptr,
-                             GM_ACT_NONE, 0.f, 0.f, 0.f);
-        return vl_launch(gemm_batched_bf16_mma_kernel<16, float>, grid, dim3(128), 0, s, (const bf16*)A, (const bf16*)W, C, M, N, K,
-                         K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll, (const int*)nullptr, 1, (const float*)nullptr,
-                         GM_ACT_NONE, 0.f, 0.f, 0.f);
+        return launch_mma_kernel<16, float>(grid, s, (const bf16*)A, (const bf16*)W, C, M, N, Kc, K, K, N, (long long)Kc,
+                                            (long long)Kc, cs, (const int*)nullptr, 0ll, (const int*)nullptr, 1,
+                                            (const float*)nullptr, GM_ACT_NONE, 0.f, 0.f, 0.f);
     }
-#define ROWS_CASE(TA, TWV, BMV)                                                                                     \
-    return vl_launch(gemm_batched_nt_kernel<TA, TWV, float, BMV>, grid, dim3(256), 0, s, (const TA*)A, (const TWV*)W, C, M, N, \
-                     K, K, K, N, 0ll, 0ll, 0ll, (const int*)nullptr, 0ll)
-    if (a_dtype == VL_F32 && w_dtype == VL_F32) { if (bm == 64) ROWS_CASE(float, float, 64); ROWS_CASE(float, float, 16); }
-    if (a_dtype == VL_BF16 && w_dtype == VL_F32) { if (bm == 64) ROWS_CASE(bf16, float, 64); ROWS_CASE(bf16, float, 16); }
-    if (a_dtype == VL_BF16 && w_dtype == VL_BF16) { if (bm == 64) ROWS_CASE(bf16, bf16, 64); ROWS_CASE(bf16, bf16, 16); }
+#define ROWS_CASE(TA, TWV)                                                                                          \
+    return vl_launch(gemm_batched_nt_kernel<TA, TWV, float, 16>, grid, dim3(256), 0, s, (const TA*)A, (const TWV*)W, C, M, N, \
+                     Kc, K, K, N, (long long)Kc, (long long)Kc, cs, (const int*)nullptr, 0ll)
+    if (a_dtype == VL_F32 && w_dtype == VL_F32) ROWS_CASE(float, float);
+    if (a_dtype == VL_BF16 && w_dtype == VL_F32) ROWS_CASE(bf16, float);
+    if (a_dtype == VL_BF16 && w_dtype == VL_BF16) ROWS_CASE(bf16, bf16);
 #undef ROWS_CASE
     return VL_ERR_UNSUPPORTED;
 }

@@ -25,7 +25,7 @@
 
 // one warp per token; z [ntok, E]: the router's logits (csrc/gemm_batched.cu: vl_gemm_rows_f32w)
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, int ntok, int E, int top,
+moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int top,
                  int score_fn, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float s_scores[];                  // [4][E]
     pdl_launch_dependents();
@@ -34,7 +34,11 @@ moe_route_kernel(const float* __restrict__ z, int ntok, int E, int top,
     const int t = blockIdx.x * 4 + warp;
     if (t >= ntok) return;
     float* sc = s_scores + (size_t)warp * E;
-    for (int e = lane; e < E; e += 32) sc[e] = z[(size_t)t * E + e];
+    for (int e = lane; e < E; e += 32) {                 // the logits came as sums over slices of K: added in their order
+        float v = 0.f;
+        for (int sl = 0; sl < slices; ++sl) v += z[((size_t)sl * ntok + t) * E + e];
+        sc[e] = v;
+    }
     __syncwarp();
     // The choice is made on the logits: both score functions grow with z, and a sigmoid that has
     // rounded to 1 for several experts would hide which of them is the largest.
@@ -134,7 +138,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    for (int n = blockIdx.y * blockDim.x + threadIdx.x; n < N; n += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j) {
             const int r = place[(size_t)t * top + j];
@@ -146,13 +150,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
     }
 }
 
-extern "C" int vl_moe_route(const float* z, int T, int E, int top, int score_fn, int renorm, int* ids, float* weights,
-                            void* stream) {
+extern "C" int vl_moe_route(const float* z, int slices, int T, int E, int top, int score_fn, int renorm, int* ids,
+                            float* weights, void* stream) {
     if (T <= 0) return VL_OK;
-    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E) return VL_ERR_ARGUMENT;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || slices <= 0) return VL_ERR_ARGUMENT;
     if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
     return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream,
-                     z, T, E, top, score_fn, renorm, ids, weights);
+                     z, slices, T, E, top, score_fn, renorm, ids, weights);
 }
 
 // cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)
@@ -186,10 +190,10 @@ extern "C" int vl_moe_combine(const void* result, int dtype, const int* place, c
     if (top <= 0 || N <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        return vl_launch(moe_combine_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)result, place, weights, top, N,
+        return vl_launch(moe_combine_kernel<float>, dim3(T, (N + 511) / 512), dim3(128), 0, s, (const float*)result, place, weights, top, N,
                          scale_output, (float*)out);
     if (dtype == VL_BF16)
-        return vl_launch(moe_combine_kernel<bf16>, dim3(T), dim3(128), 0, s, (const bf16*)result, place, weights, top, N,
+        return vl_launch(moe_combine_kernel<bf16>, dim3(T, (N + 511) / 512), dim3(128), 0, s, (const bf16*)result, place, weights, top, N,
                          scale_output, (bf16*)out);
     return VL_ERR_UNSUPPORTED;
 }

@@ -74,8 +74,8 @@ _SIGNATURES = {
     ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                                 c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
                                                 c_void_p],
-    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-    ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                        c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
     ("moe", "vl_moe_align"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -690,23 +690,33 @@ def moe_sorted_rows(npairs, num_experts, bm) -> int:
     return -(-need // bm) * bm
 
 
+def router_slices(K) -> int:
+    """Parts into which the router's product cuts K (each a block's share; the parts' sums are added in order).
+    A function of K alone, so that a token's logits do not depend on the step it is in."""
+    for parts in (8, 4, 2):
+        if K % (parts * 256) == 0:
+            return parts
+    return 1
+
+
 def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False):
     """h [T, K], router [E, K] (float32; or bfloat16 as stored, beside bfloat16 rows: products of two bfloat16 numbers
     are exact in float32, so the tensor cores' float32 sums are the 32-bit logits of the rounded rows):
-    logits float32 [T, E] = h router^T; ids int32 [T, top] = the experts with
+    logits float32 [router_slices(K), T, E] = partial sums of h router^T; ids int32 [T, top] = the experts with
     the largest logits, weights float32 [T, top] = their scores (divided by their sum when `renormalize`)."""
-    _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 2)
+    _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 3)
     if router.dtype != torch.float32 and router.dtype != h.dtype:
         raise KernelError("moe_route: the router is float32, or bfloat16 beside bfloat16 rows")
     _need(ids, torch.int32, "ids", 2); _need(weights, torch.float32, "weights", 2)
     T, K = h.shape
     E = router.shape[0]
-    if router.shape[1] != K or ids.shape != (T, top) or weights.shape != (T, top) or logits.shape != (T, E):
-        raise KernelError("moe_route: shapes disagree")
+    slices = router_slices(K)
+    if router.shape[1] != K or ids.shape != (T, top) or weights.shape != (T, top) or logits.shape != (slices, T, E):
+        raise KernelError("moe_route: shapes disagree (logits: [router_slices(K), T, E])")
     _check(_fn("gemm_batched", "vl_gemm_rows_f32w")(_ptr(h), dtype_code(h.dtype), _ptr(router), dtype_code(router.dtype),
-                                                    _ptr(logits), T, E, K, _stream()), "vl_gemm_rows_f32w")
-    _check(_fn("moe", "vl_moe_route")(_ptr(logits), T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)), _ptr(ids),
-                                      _ptr(weights), _stream()), "vl_moe_route")
+                                                    _ptr(logits), T, E, K, slices, _stream()), "vl_gemm_rows_f32w")
+    _check(_fn("moe", "vl_moe_route")(_ptr(logits), slices, T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)),
+                                      _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
 
 
 TC5_GROUPED_TILE = 128    # rows per tile of the grouped tcgen05 product

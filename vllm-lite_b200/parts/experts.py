@@ -76,14 +76,16 @@ class RoutedExperts:
         T, E, top, I, H = h.shape[0], s.num_experts, s.top, s.intermediate_size, s.hidden_size
         pairs = T * top
         big = self.fused and ops.gemm_grouped_tc5_ok(self.dtype, pairs, E, H) and I % 8 == 0
-        bm = ops.TC5_GROUPED_TILE if big else (16 if pairs <= SMALL_STEP_PAIRS else 64)
+        # tiles of 16 rows while an expert gets 16 rows or fewer on average (decoding: the products are then bound
+        # by the experts' weights, and taller tiles would spend their time on rows of padding)
+        bm = ops.TC5_GROUPED_TILE if big else (16 if pairs <= max(SMALL_STEP_PAIRS, 16 * E) else 64)
         cap = ops.moe_sorted_rows(pairs, E, bm)
         ids = ws.get(tag + "moe.ids", (T, top), torch.int32)
         weights = ws.get(tag + "moe.weights", (T, top), torch.float32)
         sorted_rows = ws.get(tag + "moe.sorted", (cap,), torch.int32)
         tile_group = ws.get(tag + "moe.tiles", (cap // bm,), torch.int32)
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
-        logits = ws.get(tag + "moe.logits", (T, E), torch.float32)
+        logits = ws.get(tag + "moe.logits", (ops.router_slices(H), T, E), torch.float32)
         ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
         act = ws.get(tag + "moe.act", (cap, I), self.dtype)
