@@ -177,6 +177,64 @@ layernorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ w, floa
     }
 }
 
+// The same with the row of y kept in registers (H a multiple of 4, at most 256 * 4 * VPT values): one read of y,
+// one read and one write of x, one write of the cast, 16-byte accesses.  Thread i holds the pieces i, i + 256, ...
+template <typename TA, int VPT>
+__global__ void __launch_bounds__(256)
+layernorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
+                         TA* __restrict__ cast, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, H4 = H >> 2;
+    const TA* yr = y + (size_t)r * H;
+    float4 v[VPT];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < H4) {
+            v[i] = Quad<TA>::load(yr + 4 * c);
+            s += v[i].x; s += v[i].y; s += v[i].z; s += v[i].w;
+        }
+    }
+    const float mean = block_sum<256>(s, scratch) / (float)H;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < H4) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            ss += v[i].x * v[i].x; ss += v[i].y * v[i].y; ss += v[i].z * v[i].z; ss += v[i].w * v[i].w;
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
+    float* xr = x + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < H4) {
+            const float4 g = Quad<float>::load(w + 4 * c);
+            float4 o = Quad<float>::load(xr + 4 * c);
+            o.x += v[i].x * inv * g.x; o.y += v[i].y * inv * g.y; o.z += v[i].z * inv * g.z; o.w += v[i].w * inv * g.w;
+            Quad<float>::store(xr + 4 * c, o);
+            if (cast) Quad<TA>::store(cast + (size_t)r * H + 4 * c, o);
+        }
+    }
+}
+
+template <typename TA>
+static bool launch_layernorm_add_vec(const TA* y, const float* w, float eps, float* x, TA* cast, int R, int H, cudaStream_t s) {
+    if (H % 4) return false;
+    const int pieces = (H / 4 + 255) / 256;
+    if (pieces <= 1) vl_launch(layernorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, w, eps, x, cast, H);
+    else if (pieces <= 2) vl_launch(layernorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, w, eps, x, cast, H);
+    else if (pieces <= 4) vl_launch(layernorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, w, eps, x, cast, H);
+    else if (pieces <= 8) vl_launch(layernorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, w, eps, x, cast, H);
+    else return false;
+    return true;
+}
+
 template <typename TA>
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
@@ -200,10 +258,14 @@ extern "C" int vl_layernorm_add(const void* y, int act_dtype, const float* w, fl
     if (R <= 0) return VL_OK;
     if (H <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == VL_F32)
+    if (act_dtype == VL_F32) {
+        if (launch_layernorm_add_vec<float>((const float*)y, w, eps, x, (float*)cast, R, H, s)) return vl_launch_status();
         return vl_launch(layernorm_add_kernel<float>, dim3(R), dim3(256), 0, s, (const float*)y, w, eps, x, (float*)cast, H);
-    if (act_dtype == VL_BF16)
+    }
+    if (act_dtype == VL_BF16) {
+        if (launch_layernorm_add_vec<bf16>((const bf16*)y, w, eps, x, (bf16*)cast, R, H, s)) return vl_launch_status();
         return vl_launch(layernorm_add_kernel<bf16>, dim3(R), dim3(256), 0, s, (const bf16*)y, w, eps, x, (bf16*)cast, H);
+    }
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -141,12 +141,12 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
                              int lda, int ldw, int ldc, long long a_bs, long long w_bs, long long c_bs,
                              const int* __restrict__ tile_group, long long w_gs,
                              const int* __restrict__ row_index, int index_div, const float* __restrict__ row_scale,
-                             int act, float alpha, float limit, float shift) {
+                             int act, float alpha, float limit, float shift, int nst) {
     constexpr int WARPS_M = BM / 16, WARPS_N = 4 / WARPS_M, WN = GM_BN / WARPS_N, NT = WN / 8;
     // the ring is larger than the 48 KB a kernel may declare: dynamic shared memory
     extern __shared__ __align__(16) unsigned char gm_smem[];
     bf16 (*As)[BM][GM_LDS] = reinterpret_cast<bf16 (*)[BM][GM_LDS]>(gm_smem);
-    bf16 (*Ws)[GM_BN][GM_LDS] = reinterpret_cast<bf16 (*)[GM_BN][GM_LDS]>(gm_smem + (size_t)GM_NST * BM * GM_LDS * sizeof(bf16));
+    bf16 (*Ws)[GM_BN][GM_LDS] = reinterpret_cast<bf16 (*)[GM_BN][GM_LDS]>(gm_smem + (size_t)nst * BM * GM_LDS * sizeof(bf16));
     __shared__ int s_src[BM];                                    // source row of every row of the tile (-1: zeros)
     pdl_launch_dependents();
     pdl_wait();
@@ -192,18 +192,18 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
             gm_cp_async16(&Ws[st][r][c * 8], ok ? Wb + (size_t)(n0 + r) * ldw + k : Wb, ok);
         }
     };
-#pragma unroll
-    for (int s = 0; s < GM_NST - 1; ++s) {
+    // nst stages (2 to GM_NST: a short K needs no long ring, and a short ring lets more blocks share an SM)
+    for (int s = 0; s < nst - 1; ++s) {
         if (s < KT) load_stage(s, s);
         gm_commit();
     }
     for (int kt = 0; kt < KT; ++kt) {
-        gm_wait<GM_NST - 2>();
+        if (nst == 2) gm_wait<0>(); else if (nst == 3) gm_wait<1>(); else gm_wait<2>();
         __syncthreads();
-        const int nk = kt + GM_NST - 1;
-        if (nk < KT) load_stage(nk % GM_NST, nk);
+        const int nk = kt + nst - 1;
+        if (nk < KT) load_stage(nk % nst, nk);
         gm_commit();
-        const int st = kt % GM_NST;
+        const int st = kt % nst;
 #pragma unroll
         for (int kk = 0; kk < GM_BK / 16; ++kk) {
             unsigned a[4];
@@ -219,6 +219,7 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
     }
     gm_wait<0>();
     const int g = lane >> 2, t2 = (lane & 3) * 2;
+    const bool pair_ok = ((ldc | c_bs) & 1) == 0 && (((uintptr_t)C) & 3) == 0;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int r = wm * 16 + g + half * 8;
@@ -235,8 +236,13 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
             for (int nt = 0; nt < NT; ++nt) {
                 const int n = n0 + wn * WN + nt * 8 + t2;
                 const float v0 = acc[nt][2 * half] * scale, v1 = acc[nt][2 * half + 1] * scale;
-                if (n < N) crow[n] = from_f32<TC>(v0);
-                if (n + 1 < N) crow[n + 1] = from_f32<TC>(v1);
+                if (sizeof(TC) == 2 && pair_ok && n + 1 < N) {          // two bfloat16 in one 4-byte store
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);
+                    *reinterpret_cast<unsigned*>(crow + n) = *reinterpret_cast<unsigned*>(&pr);
+                } else {
+                    if (n < N) crow[n] = from_f32<TC>(v0);
+                    if (n + 1 < N) crow[n + 1] = from_f32<TC>(v1);
+                }
             }
         } else {
             // n-tiles come in pairs: 8 gate columns, then their 8 up columns; the pair writes 8 columns
@@ -254,16 +260,19 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
 }
 
 template <int BM, typename TC, typename... Args>
-static int launch_mma_kernel(dim3 grid, cudaStream_t s, Args... args) {
-    const size_t smem = (size_t)GM_NST * (BM + GM_BN) * GM_LDS * sizeof(bf16);
+static int launch_mma_kernel(dim3 grid, cudaStream_t s, int K, Args... args) {
+    const int KT = (K + GM_BK - 1) / GM_BK;
+    const int nst = KT < 2 ? 2 : (KT > GM_NST ? GM_NST : KT);
+    const size_t most = (size_t)GM_NST * (BM + GM_BN) * GM_LDS * sizeof(bf16);
+    const size_t smem = (size_t)nst * (BM + GM_BN) * GM_LDS * sizeof(bf16);
     auto kern = gemm_batched_bf16_mma_kernel<BM, TC>;
     static bool ready = false;                               // per instantiation
     if (!ready) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
         if (e != cudaSuccess) return (int)e;
         ready = true;
     }
-    return vl_launch(kern, grid, dim3(128), smem, s, args...);
+    return vl_launch(kern, grid, dim3(128), smem, s, args..., nst);
 }
 
 static bool gm_aligned(const void* A, const void* W, int K, int lda, int ldw, long long a_bs, long long w_bs, long long w_gs) {
@@ -277,9 +286,9 @@ static int launch_batched_mma(const bf16* A, const bf16* W, bf16* C, int M, int 
     dim3 grid((N + GM_BN - 1) / GM_BN, (M + bm - 1) / bm, batch);
     if (grid.y > 65535 || grid.z > 65535) return VL_ERR_UNSUPPORTED;
     if (bm == 64)
-        return launch_mma_kernel<64, bf16>(grid, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
+        return launch_mma_kernel<64, bf16>(grid, s, K, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
                                            row_index, index_div, row_scale, act, alpha, limit, shift);
-    return launch_mma_kernel<16, bf16>(grid, s, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
+    return launch_mma_kernel<16, bf16>(grid, s, K, A, W, C, M, N, K, lda, ldw, ldc, a_bs, w_bs, c_bs, tile_group, w_gs,
                                        row_index, index_div, row_scale, act, alpha, limit, shift);
 }
 
@@ -333,7 +342,7 @@ extern "C" int vl_gemm_rows_f32w(const void* A, int a_dtype, const void* W, int 
     cudaStream_t s = (cudaStream_t)stream;
     if (a_dtype == VL_BF16 && w_dtype == VL_BF16 && gm_aligned(A, W, Kc, K, K, Kc, Kc, 0) && !vl_batched_simt_only()) {
         // both operands bfloat16: their products are exact in float32, the tensor cores add them in float32
-        return launch_mma_kernel<16, float>(grid, s, (const bf16*)A, (const bf16*)W, C, M, N, Kc, K, K, N, (long long)Kc,
+        return launch_mma_kernel<16, float>(grid, s, Kc, (const bf16*)A, (const bf16*)W, C, M, N, Kc, K, K, N, (long long)Kc,
                                             (long long)Kc, cs, (const int*)nullptr, 0ll, (const int*)nullptr, 1,
                                             (const float*)nullptr, GM_ACT_NONE, 0.f, 0.f, 0.f);
     }
