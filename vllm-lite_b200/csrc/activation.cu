@@ -75,6 +75,39 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     out[idx] = from_f32<T>(r);
 }
 
+// The plain-halves layout (group 0) with I a multiple of 8: eight outputs a thread, 16-byte accesses.
+template <typename T>
+__global__ void gated_act_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total8, int act,
+                                     float alpha, float limit, float shift, const float* __restrict__ bias) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const int per_row = I / 8;
+    const size_t t = idx / per_row;
+    const int i = (int)(idx - t * per_row) * 8;
+    float g[8], u[8], r[8];
+    load8(gu + t * 2 * (size_t)I + i, g);
+    load8(gu + t * 2 * (size_t)I + I + i, u);
+    if (bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { g[e] += bias[i + e]; u[e] += bias[I + i + e]; }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float gg = g[e], uu = u[e];
+        if (act == VL_ACT_RELU) {
+            r[e] = fmaxf(gg, 0.f) * uu;
+        } else if (act == VL_ACT_CAPPED_SWISH) {
+            if (limit > 0.f) { gg = fminf(gg, limit); uu = fminf(fmaxf(uu, -limit), limit); }
+            r[e] = gg / (1.0f + expf(-alpha * gg)) * (uu + shift);
+        } else {
+            r[e] = gg / (1.0f + expf(-gg)) * uu;
+        }
+    }
+    store8(out + t * (size_t)I + i, r);
+}
+
 extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, int group, int act, float alpha,
                             float limit, float shift, const float* bias, void* stream) {
     if (T <= 0 || I <= 0) return VL_OK;
@@ -82,6 +115,16 @@ extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     const size_t total = (size_t)T * I;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
+    if (group == 0 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+        const size_t total8 = total / 8;
+        const unsigned b8 = (unsigned)((total8 + 255) / 256);
+        if (dtype == VL_F32)
+            return vl_launch(gated_act_vec_kernel<float>, dim3(b8), dim3(256), 0, s, (const float*)gu, (float*)out, I, total8, act,
+                             alpha, limit, shift, bias);
+        if (dtype == VL_BF16)
+            return vl_launch(gated_act_vec_kernel<bf16>, dim3(b8), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, total8, act,
+                             alpha, limit, shift, bias);
+    }
     if (dtype == VL_F32)
         return vl_launch(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total, group,
                          act, alpha, limit, shift, bias);

@@ -128,6 +128,18 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict
     }
     const T* src = h + (size_t)(p / top) * K;
     const float w = scale_input ? weights[p] : 1.0f;
+    if (K % 8 == 0) {                                    // rows start on 16-byte boundaries: eight values an access
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+            float v[8];
+            load8(src + k, v);
+            if (scale_input) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] *= w;
+            }
+            store8(dst + k, v);
+        }
+        return;
+    }
     for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = scale_input ? from_f32<T>(w * to_f32(src[k])) : src[k];
 }
 
@@ -138,6 +150,22 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
+    if (N % 8 == 0) {                                    // eight columns a thread, 16-byte accesses
+        for (int n = (blockIdx.y * blockDim.x + threadIdx.x) * 8; n < N; n += gridDim.y * blockDim.x * 8) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < top; ++j) {
+                const int r = place[(size_t)t * top + j];
+                if (r < 0) continue;
+                float v[8];
+                load8(result + (size_t)r * N + n, v);
+                const float w = scale_output ? weights[(size_t)t * top + j] : 1.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += scale_output ? w * v[i] : v[i];
+            }
+            store8(out + (size_t)t * N + n, acc);
+        }
+        return;
+    }
     for (int n = blockIdx.y * blockDim.x + threadIdx.x; n < N; n += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j) {
