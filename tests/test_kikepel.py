@@ -57,8 +57,13 @@ CONFIGS = {
               layers=[layer("latent_attention", mixer(8, 32, 48, 64, 128, 200), moe(64, 8, 2, 1.5)),
                       layer("latent_attention_2", mixer(4, 64, 64, 96, 128, 70), dense(160))]),
 }
-PAGE = {"U": 8, "V": 16, "W": 64}
-SEED = {"U": 11, "V": 12, "W": 13}
+# X: the smallest and the largest sizes the kernels take side by side: one head of 8 numbers, a cached row of 256, a
+# window longer than any prompt, an expert width that is no multiple of 8, a vocabulary and a width that are no powers of two
+CONFIGS["X"] = dict(architecture="Kikepel", vocab=97, width=72, norm=dict(eps=2e-5), logit_scale=1.0, logit_softcap=20.0,
+                    layers=[layer("latent_attention", mixer(1, 8, 8, 8, 256, 300), moe(20, 5, 2, 3.0)),
+                            layer("latent_attention_2", mixer(3, 8, 40, 56, 8, 5, scale=0.9), dense(24))])
+PAGE = {"U": 8, "V": 16, "W": 64, "X": 4}
+SEED = {"U": 11, "V": 12, "W": 13, "X": 14}
 TOL = {"float32": 3e-5, "bfloat16": 4e-2}
 
 
@@ -496,8 +501,8 @@ def test_a_sink_and_a_far_key_show_in_the_attention():
 # the model in the engine
 # ----------------------------------------------------------------------------------------------
 
-CASES = [(w, d) for w in ("U", "V", "W") for d in ("float32", "bfloat16")]
-LENGTHS = {"U": [1, 6, 8, 9, 40, 75], "V": [2, 17, 33, 120, 170], "W": [65, 230, 300]}
+CASES = [(w, d) for w in ("U", "V", "W", "X") for d in ("float32", "bfloat16")]
+LENGTHS = {"U": [1, 6, 8, 9, 40, 75], "V": [2, 17, 33, 120, 170], "W": [65, 230, 300], "X": [1, 3, 50, 131]}
 
 
 @pytest.mark.gpu
@@ -535,7 +540,7 @@ def test_residual_stream_after_every_layer(which):
 @pytest.mark.parametrize("which,dtype", CASES)
 def test_prompt_then_token_by_token(which, dtype):
     """Most of a request in one step, then single tokens until every window has passed over decoded tokens."""
-    length, tail = {"U": (90, 40), "V": (260, 170), "W": (300, 90)}[which]
+    length, tail = {"U": (90, 40), "V": (260, 170), "W": (300, 90), "X": (60, 20)}[which]
     toks = tokens_for(which, length, 7)
     runner = make_runner(which, dtype, num_pages=pages_for(which, length + PAGE[which]))
     head = length - tail
@@ -558,7 +563,7 @@ def test_first_tokens_one_by_one(which, dtype):
 @pytest.mark.gpu
 @pytest.mark.parametrize("which,dtype", CASES)
 def test_portions_of_changing_size(which, dtype):
-    length = {"U": 120, "V": 200, "W": 330}[which]
+    length = {"U": 120, "V": 200, "W": 330, "X": 90}[which]
     toks = tokens_for(which, length, 11)
     runner = make_runner(which, dtype, num_pages=pages_for(which, length + PAGE[which]))
     sizes = [7, 2, 13, 3, 2, 16, 5, 2, 31, 8, 2, 17, 2, 2, 3] if which != "W" else [70, 2, 129, 3, 64, 2, 40, 2, 2, 16]
@@ -718,3 +723,47 @@ def test_greedy_generation_bfloat16_follows_the_plain_logits():
             far += float(row.max() - row[t]) > 2 * TOL["bfloat16"] * float(row.abs().max())
             toks.append(t)
     assert far <= 1
+
+
+@pytest.mark.gpu
+def test_command_line_and_replay_program(tmp_path):
+    """`python -m vllm_lite_b200 init` writes a Kikepel folder from its config.json, the command line generates from it
+    (greedy, float32: the plain implementation's tokens), and bin/trace_run replays steps on it."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(CONFIGS["U"]))
+    folder = tmp_path / "model"
+    run = lambda *a, **k: subprocess.run([sys.executable, *a], capture_output=True, text=True, cwd=root, timeout=900, **k)
+    made = run("-m", "vllm_lite_b200", "init", "--config", str(cfg), "--out", str(folder), "--seed", "5", "--std", "0.08")
+    assert made.returncode == 0, made.stderr[-2000:]
+    prompt = tokens_for("U", 14, 77)
+    out = run("-m", "vllm_lite_b200", "--model", str(folder), "--dtype", "float32", "--kv-blocks", "32", "--max-tokens", "6",
+              "--prompt-ids", ",".join(map(str, prompt)), "--log-level", "warn")
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = [int(t) for t in out.stdout.strip().split(",")]
+    pc, pw = P.read_model_dir(folder)
+    toks = list(prompt)
+    for t in got:
+        row = P.forward(pc, pw, toks)[-1]
+        assert int(row.argmax()) == t or float(row.max() - row[t]) < 1e-4 * float(row.abs().max())
+        toks.append(t)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": prompt[:9], "want": [8]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": prompt[9:], "want": [0, 4]}, {"id": "b", "tokens": [3, 1], "want": []}],
+              "end": ["a"]},
+             {"step": 2, "entries": [{"id": "b", "tokens": [4], "want": [0]}], "end": ["b"]}]
+    outdir = tmp_path / "logits"
+    rep = run(str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(outdir),
+              "--max-tokens", "64", "--page-size", "8", input="".join(json.dumps(x) + "\n" for x in steps))
+    assert rep.returncode == 0, rep.stderr[-2000:]
+    assert [l for l in rep.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ref = P.forward(pc, pw, prompt).float()
+    rows = np.fromfile(outdir / "1.f32", dtype="<f4").reshape(2, CONFIGS["U"]["vocab"])
+    for row, pos in zip(rows, (9, 13)):
+        assert float(np.abs(row - ref[pos].numpy()).max()) <= TOL["float32"] * float(ref[pos].abs().max())
+    last = np.fromfile(outdir / "2.f32", dtype="<f4")
+    refb = P.forward(pc, pw, [3, 1, 4]).float()[2].numpy()
+    assert float(np.abs(last - refb).max()) <= TOL["float32"] * float(np.abs(refb).max())
