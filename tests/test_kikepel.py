@@ -233,6 +233,23 @@ def test_latent_layers_share_pools_by_width_and_window():
     mgr.check_invariants()
 
 
+def test_cache_sized_from_memory_for_latent_groups():
+    """The arithmetic of `kv_blocks=None` on a plan of latent layers and experts: groups are capped by what their
+    window lets a request hold, and a latent page costs one plane of its row width."""
+    from vllm_lite_b200.cache.manager import CacheLayout
+    from vllm_lite_b200.cache.sizing import activation_reserve, page_bytes, pages_from_memory
+    from vllm_lite_b200.config import plan_from_config_json
+    from vllm_lite_b200.parts.model import cache_needs
+    _, plan = plan_from_config_json(CONFIGS["V"])
+    layout = CacheLayout.from_needs(cache_needs(plan), [None] * 4)
+    assert page_bytes(layout, 16, 2) == [16 * 64 * 2, 16 * 112 * 2, 16 * 16 * 2, 16 * 48 * 2]
+    reserve = activation_reserve(plan, 512, 4, 1024, 2)
+    assert reserve > 0
+    pages = pages_from_memory(layout, 16, 2, 8 << 30, 0.9, reserve, 4, 1024, 512)
+    # windows 33, 100, 1, 150 and steps of up to 512 tokens: a request holds at most ceil((window + 512) / 16) + 1 pages
+    assert pages == [4 * (-(-(w + 512) // 16) + 1) + 1 for w in (33, 100, 1, 150)]
+
+
 def test_plain_softmax_sink_and_window():
     s = torch.tensor([[[0.3, -1.0, 2.0], [0.1, 0.2, 0.3], [1.0, 1.0, 1.0]]], dtype=torch.float64)
     mask = P.window_mask(3, 2)
@@ -712,7 +729,8 @@ def test_greedy_generation_bfloat16_follows_the_plain_logits():
     from vllm_lite_b200 import LLMEngine
     which = "W"
     prompts = [tokens_for(which, n, 60 + i) for i, n in enumerate([9, 140])]
-    eng = LLMEngine(str(model_dir(which, "bfloat16")), dtype="bfloat16", kv_blocks=16, block_size=64, max_batch_size=4,
+    # kv_blocks=None: the cache is sized from the GPU's free memory (capped by what 4 requests of 512 tokens can hold)
+    eng = LLMEngine(str(model_dir(which, "bfloat16")), dtype="bfloat16", kv_blocks=None, block_size=64, max_batch_size=4,
                     max_model_len=512)
     outs = eng.generate(prompts, max_tokens=12)
     far = 0

@@ -42,9 +42,17 @@ def activation_reserve(plan, max_step_tokens: int, max_requests: int, max_contex
     for block in plan.layers:
         w = 0
         mixer, ffn = getattr(block, "mixer", None), getattr(block, "ffn", None)
-        if hasattr(mixer, "num_heads"):
+        if hasattr(mixer, "num_kv_heads"):
             w += (2 * mixer.num_heads + 2 * mixer.num_kv_heads) * mixer.head_dim
-        if hasattr(ffn, "intermediate_size"):
+        elif hasattr(mixer, "kv_rank"):
+            # latent attention: both latents, the queries, their absorbed form and the context (heads x cached row, the
+            # row rounded up to 16), the expanded values
+            row = -(-mixer.kv_rank // 16) * 16
+            w += mixer.q_rank + mixer.kv_rank + mixer.num_heads * (mixer.dim + 2 * row + mixer.vdim)
+        if hasattr(ffn, "top"):
+            # routed experts: every token's row `top` times (sorted copy, gate and up, activation, result), tiles padded
+            w += 2 * ffn.top * (3 * ffn.intermediate_size + 2 * H)
+        elif hasattr(ffn, "intermediate_size"):
             w += 3 * ffn.intermediate_size
         widest = max(widest, w)
     per_token = 4 * H + itemsize * (widest + 4 * H)

@@ -30,7 +30,8 @@ from .spec import LatentAttentionSpec, TensorDecl
 MAX_LATENT = 256            # widest cached row the attention kernels take
 
 # what the attention dispatcher reads of a mixer's description
-HeadLayout = namedtuple("HeadLayout", "num_heads num_kv_heads head_dim window")
+# (shared_row: keys and values are the same rows of one shared head, which the choice of the decode chunks may use)
+HeadLayout = namedtuple("HeadLayout", "num_heads num_kv_heads head_dim window shared_row", defaults=(False,))
 
 
 def padded_rank(kv_rank: int) -> int:
@@ -92,7 +93,7 @@ class LatentAttention:
         self.o = Linear(weights[o])
         self.sinks = weights[sink].to(device=ctx.device, dtype=torch.float32).contiguous() if spec.sink else None
         self.scale = spec.scale if spec.scale is not None else D ** -0.5
-        self.layout = HeadLayout(H, 1, self.rank, spec.window)
+        self.layout = HeadLayout(H, 1, self.rank, spec.window, True)
 
     def __call__(self, h, step, cache):
         from ..csrc import ops
