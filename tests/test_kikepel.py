@@ -337,12 +337,18 @@ def test_latent_norms_and_cache_write(dtype, q_rank, kv_rank, width):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,heads,N,K", [(1, 3, 48, 16), (13, 5, 20, 33), (150, 2, 130, 64), (70, 12, 16, 128)])
-def test_products_per_head(dtype, T, heads, N, K):
+def test_products_per_head(dtype, T, heads, N, K, monkeypatch):
+    """K = 33 takes the FFMA kernel in both dtypes; the other bfloat16 cases the tensor cores, and once more the FFMA
+    kernel (the switch that keeps bfloat16 products off the tensor cores): both against the same sums."""
     a, w = rand((T, heads * K), 7, dtype), rand((heads, N, K), 8, dtype)
     out = torch.empty((T, heads * N), dtype=dtype, device=DEV)
     ops().gemm_heads(a, w, out)
     want = torch.einsum("thk,hnk->thn", a.double().view(T, heads, K), w.double()).reshape(T, heads * N)
     close(out, want, dtype, "per-head product")
+    monkeypatch.setenv("VLLM_LITE_B200_BATCHED_SIMT", "1")
+    again = torch.empty_like(out)
+    ops().gemm_heads(a, w, again)
+    close(again, want, dtype, "per-head product, FFMA kernel")
 
 
 @pytest.mark.gpu
