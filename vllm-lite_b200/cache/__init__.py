@@ -1,7 +1,7 @@
 """Paged key/value cache, per-request state slots and their device storage."""
 from .manager import CacheLayout, CacheManager, OutOfPages, RequestCache  # noqa: F401
 from .pool import Pool, PoolError  # noqa: F401
-from .spec import FixedState, PagedKV, PagedLatent  # noqa: F401
+from .spec import FixedState, PagedKV, PagedLatent, Several  # noqa: F401
 
 
 def make_cache_manager(layout, page_size, num_pages, max_requests, native=True):

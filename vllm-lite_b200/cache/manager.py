@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 from .pool import Pool, PoolError
-from .spec import FixedState, PagedKV, PagedLatent
+from .spec import FixedState, PagedKV, PagedLatent, Several
 
 
 @dataclass
@@ -30,23 +30,22 @@ class CacheLayout:
     paged_members: List[List[int]]          # order indices that own a cache in the group
     state_groups: List[FixedState]
     state_members: List[List[int]]
-    call_place: List[Optional[tuple]]       # per order entry: ("paged"|"state", group, index in group, owns)
+    call_place: List[Optional[tuple]]       # per order entry: ("paged"|"state", group, index in group, owns),
+                                            # or ("several", [such places]) for a call with more than one need
 
     @classmethod
     def from_needs(cls, needs: list, cache_of: list) -> "CacheLayout":
         pg, pm, sg, sm = [], [], [], []
         place: List[Optional[tuple]] = [None] * len(needs)
-        for i, need in enumerate(needs):
-            if cache_of[i] is not None:
-                continue
-            if need is None:
-                continue
+
+        def put(i, need):
             if isinstance(need, (PagedKV, PagedLatent)):
                 groups, members, kind = pg, pm, "paged"
             elif isinstance(need, FixedState):
                 groups, members, kind = sg, sm, "state"
             else:
-                raise TypeError(f"order[{i}] asks for {need!r}; a cache need is PagedKV, PagedLatent, FixedState or None")
+                raise TypeError(f"order[{i}] asks for {need!r}; a cache need is PagedKV, PagedLatent, FixedState, "
+                                f"Several of them or None")
             if need in groups:
                 g = groups.index(need)
             else:
@@ -54,13 +53,24 @@ class CacheLayout:
                 members.append([])
                 g = len(groups) - 1
             members[g].append(i)
-            place[i] = (kind, g, len(members[g]) - 1, True)
+            return (kind, g, len(members[g]) - 1, True)
+
+        for i, need in enumerate(needs):
+            if cache_of[i] is not None or need is None:
+                continue
+            if isinstance(need, Several):
+                place[i] = ("several", [put(i, part) for part in need.parts])
+            else:
+                place[i] = put(i, need)
         for i, src in enumerate(cache_of):
             if src is not None:
                 if place[src] is None:
                     raise ValueError(f"order[{i}] reads the cache of order[{src}], which keeps none")
-                kind, g, idx, _ = place[src]
-                place[i] = (kind, g, idx, False)
+                if place[src][0] == "several":
+                    place[i] = ("several", [(kind, g, idx, False) for kind, g, idx, _ in place[src][1]])
+                else:
+                    kind, g, idx, _ = place[src]
+                    place[i] = (kind, g, idx, False)
         return cls(pg, pm, sg, sm, place)
 
 

@@ -6,6 +6,8 @@ pages that lie wholly before the window may be given back.
 `PagedLatent`: one row per token from which keys and values are both derived (a
 compressed latent); paged and windowed like `PagedKV`, but stored once.
 `FixedState`: a tensor of fixed shape per request, stored in a slot.
+`Several`: a mixer that keeps more than one of these (two mixers side by side); every part is placed as if it
+were a call's only need, and the call's cache holds them in order (`CallCache.parts`).
 Calls of the running order whose needs are equal share one group: one pool of
 pages (or slots) and one block table per request.
 """
@@ -48,3 +50,8 @@ class PagedLatent:
 class FixedState:
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class Several:
+    parts: Tuple[object, ...]

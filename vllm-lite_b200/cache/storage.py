@@ -32,12 +32,16 @@ class CacheStorage:
         for place in layout.call_place:
             if place is None:
                 self.call_caches.append(CallCache())
-                continue
-            kind, g, idx, owns = place
-            if kind == "paged":
-                self.call_caches.append(CallCache(group=g, k=self.paged[g][idx, 0], v=self.paged[g][idx, self.paged[g].shape[1] - 1], writes=owns))
+            elif place[0] == "several":
+                self.call_caches.append(CallCache(parts=[self._call_cache(p) for p in place[1]]))
             else:
-                self.call_caches.append(CallCache(group=g, state=self.state[g][idx], writes=owns))
+                self.call_caches.append(self._call_cache(place))
+
+    def _call_cache(self, place) -> CallCache:
+        kind, g, idx, owns = place
+        if kind == "paged":
+            return CallCache(group=g, k=self.paged[g][idx, 0], v=self.paged[g][idx, self.paged[g].shape[1] - 1], writes=owns)
+        return CallCache(group=g, state=self.state[g][idx], writes=owns)
 
     def zero_slots(self, slots):
         if not slots:

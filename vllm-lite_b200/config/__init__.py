@@ -5,3 +5,4 @@ from .registry import (ArchitectureEntry, plan_from_config_json, register_archit
                        registered_architectures, resolve_architecture, unregister_architecture)
 from . import qwen3_plan as _qwen3_plan  # noqa: F401  (registers Qwen3ForCausalLM)
 from .kikepel import KikepelConfig  # noqa: F401,E402  (registers Kikepel)
+from .tuzisun import TuzisunConfig  # noqa: F401,E402  (registers Tuzisun)

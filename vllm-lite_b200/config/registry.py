@@ -57,8 +57,13 @@ def resolve_architecture(config_json: dict) -> ArchitectureEntry:
     raise UnknownArchitecture(model_type or "(no `architectures`, no `model_type`)", _REGISTRY)
 
 
-def plan_from_config_json(config_json: dict):
-    """(typed configuration, ModelPlan) for a parsed config.json."""
+def plan_from_config_json(config_json: dict, shapes: dict = None):
+    """(typed configuration, ModelPlan) for a parsed config.json.  `shapes` (tensor name -> shape, from the header
+    of the weight files) goes to a configuration class that says `needs_shapes`: some designs leave a size to
+    the tensors."""
     entry = resolve_architecture(config_json)
-    cfg = entry.config_cls.from_dict(config_json)
+    if getattr(entry.config_cls, "needs_shapes", False):
+        cfg = entry.config_cls.from_dict(config_json, shapes=shapes)
+    else:
+        cfg = entry.config_cls.from_dict(config_json)
     return cfg, entry.plan(cfg).validate()

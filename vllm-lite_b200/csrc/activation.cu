@@ -150,3 +150,23 @@ extern "C" int vl_scale_softcap(float* z, long long n, float scale, float cap, v
     const unsigned blocks = (unsigned)(((size_t)n + 255) / 256);
     return vl_launch(scale_softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, z, (size_t)n, scale, cap);
 }
+
+// out = sa * a + sb * b: what two mixers that run side by side on one input leave (float32 arithmetic).
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, T* __restrict__ out, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(sa * to_f32(a[i]) + sb * to_f32(b[i]));
+}
+
+extern "C" int vl_scaled_sum(const void* a, float sa, const void* b, float sb, void* out, int dtype, long long n, void* stream) {
+    if (n <= 0) return VL_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(scaled_sum_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
+    if (dtype == VL_BF16)
+        return vl_launch(scaled_sum_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)a, sa, (const bf16*)b, sb, (bf16*)out, (size_t)n);
+    return VL_ERR_UNSUPPORTED;
+}

@@ -26,8 +26,8 @@
 // one warp per token; z [ntok, E]: the router's logits (csrc/gemm_batched.cu: vl_gemm_rows_f32w)
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int top,
-                 int score_fn, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float s_scores[];                  // [4][E]
+                 int score_fn, int renorm, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float s_scores[];                  // [4][E], then [4][groups] when the experts form groups
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,6 +48,25 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
         zmax = warp_max(zmax);
         for (int e = lane; e < E; e += 32) zsum += expf(sc[e] - zmax);
         zsum = warp_sum(zsum);
+    }
+    if (groups > 1) {
+        // A group counts by its largest logit; experts outside the `keep` best groups (ties: the lower group) cannot
+        // be chosen.  The scores above were taken over all experts.
+        float* gm = s_scores + (size_t)4 * E + (size_t)warp * groups;
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, sc[e]);
+            gm[g] = m;
+        }
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) {
+            int ahead = 0;                               // groups that come before g in the order (larger, or equal and lower)
+            for (int o = 0; o < groups; ++o) ahead += (gm[o] > gm[g] || (gm[o] == gm[g] && o < g)) ? 1 : 0;
+            if (ahead >= keep)
+                for (int e = g * per; e < (g + 1) * per; ++e) sc[e] = -INFINITY;
+        }
+        __syncwarp();
     }
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
@@ -178,13 +197,14 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
     }
 }
 
-extern "C" int vl_moe_route(const float* z, int slices, int T, int E, int top, int score_fn, int renorm, int* ids,
-                            float* weights, void* stream) {
+extern "C" int vl_moe_route(const float* z, int slices, int T, int E, int top, int score_fn, int renorm, int groups, int keep,
+                            int* ids, float* weights, void* stream) {
     if (T <= 0) return VL_OK;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || slices <= 0) return VL_ERR_ARGUMENT;
     if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
-    return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream,
-                     z, slices, T, E, top, score_fn, renorm, ids, weights);
+    if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top) return VL_ERR_ARGUMENT;
+    return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * (E + groups) * sizeof(float),
+                     (cudaStream_t)stream, z, slices, T, E, top, score_fn, renorm, groups, keep, ids, weights);
 }
 
 // cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)

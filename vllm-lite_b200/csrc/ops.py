@@ -64,6 +64,7 @@ _SIGNATURES = {
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("activation", "vl_gated_act"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p,
                                      c_void_p],
+    ("activation", "vl_scaled_sum"): [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_longlong, c_void_p],
     ("activation", "vl_scale_softcap"): [c_void_p, c_longlong, c_float, c_float, c_void_p],
     ("embed_norm", "vl_layernorm_add"): [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("embed_norm", "vl_layernorm_rows"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -74,7 +75,7 @@ _SIGNATURES = {
     ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                                 c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
                                                 c_void_p],
-    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                        c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
@@ -96,6 +97,21 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p],
+    ("hyper", "vl_hc_step"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("hyper", "vl_dyt_rows"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("recurrent", "vl_short_conv"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
+                                     c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+    ("recurrent", "vl_ssd_scan"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("recurrent", "vl_mlstm_scan"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                     c_float, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                     c_void_p],
+    ("recurrent", "vl_delta_scan"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                     c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                     c_int, c_void_p],
+    ("recurrent", "vl_gate_norm"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p,
+                                    c_int, c_int, c_int, c_void_p],
 }
 _functions = {}
 launch_count = 0          # kernels of this library launched so far (graph replays add theirs)
@@ -558,6 +574,16 @@ def gated_act(gate_up, out, act, group=0, alpha=1.0, limit=0.0, shift=0.0, bias=
     return out
 
 
+def scaled_sum(a, scale_a, b, scale_b, out):
+    """out = scale_a * a + scale_b * b, element by element in float32; all three in one dtype and shape."""
+    _need(a, None, "a"); _need(b, a.dtype, "b"); _need(out, a.dtype, "out")
+    if a.shape != b.shape or a.shape != out.shape:
+        raise KernelError("scaled_sum: shapes differ")
+    _check(_fn("activation", "vl_scaled_sum")(_ptr(a), float(scale_a), _ptr(b), float(scale_b), _ptr(out), dtype_code(a.dtype),
+                                              a.numel(), _stream()), "vl_scaled_sum")
+    return out
+
+
 def scale_softcap(logits, scale, cap):
     """In place on float32 logits: z <- cap * tanh(z * scale / cap) (cap <= 0 or None: only the scale)."""
     _need(logits, torch.float32, "logits")
@@ -699,11 +725,13 @@ def router_slices(K) -> int:
     return 1
 
 
-def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False):
+def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False, groups=1, keep_groups=1):
     """h [T, K], router [E, K] (float32; or bfloat16 as stored, beside bfloat16 rows: products of two bfloat16 numbers
     are exact in float32, so the tensor cores' float32 sums are the 32-bit logits of the rounded rows):
     logits float32 [router_slices(K), T, E] = partial sums of h router^T; ids int32 [T, top] = the experts with
-    the largest logits, weights float32 [T, top] = their scores (divided by their sum when `renormalize`)."""
+    the largest logits, weights float32 [T, top] = their scores (divided by their sum when `renormalize`).
+    `groups` > 1: the experts form that many equal groups of neighbours, a group counts by its largest logit, and only
+    experts of the `keep_groups` best groups are chosen from (scores are still taken over all experts)."""
     _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 3)
     if router.dtype != torch.float32 and router.dtype != h.dtype:
         raise KernelError("moe_route: the router is float32, or bfloat16 beside bfloat16 rows")
@@ -715,8 +743,10 @@ def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize
         raise KernelError("moe_route: shapes disagree (logits: [router_slices(K), T, E])")
     _check(_fn("gemm_batched", "vl_gemm_rows_f32w")(_ptr(h), dtype_code(h.dtype), _ptr(router), dtype_code(router.dtype),
                                                     _ptr(logits), T, E, K, slices, _stream()), "vl_gemm_rows_f32w")
+    if groups < 1 or E % groups or not 1 <= keep_groups <= groups or keep_groups * (E // groups) < top:
+        raise KernelError(f"moe_route: {E} experts in {groups} groups, {keep_groups} kept, top {top}")
     _check(_fn("moe", "vl_moe_route")(_ptr(logits), slices, T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)),
-                                      _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
+                                      int(groups), int(keep_groups), _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
 
 
 TC5_GROUPED_TILE = 128    # rows per tile of the grouped tcgen05 product
@@ -923,3 +953,194 @@ def sample(logits, temperature, top_k, top_p, uniform, out_token, out_logprob=No
         _ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
         _ptr(out_token), _ptr(out_logprob), _stream()), "vl_sample")
     return out_token
+
+
+# ---------------------------------------------------------------- several residual streams, tanh norm
+HC_MAX_STREAMS = 8
+
+
+def hc_step(streams, *, single=None, y=None, mix=None, out_w=None, in_w=None, norm=None, h=None, total=None):
+    """One pass over the streams float32 [T, S, H] (csrc/hyper.cu): spread from `single` [T, H], write a sub-layer's
+    result `y` [T, H] back (mix [S, S] indexed [from, to], out_w [S]), read the next sub-layer's input into `h` [T, H]
+    (in_w [S]; norm = (alpha, weight, bias) of the tanh norm, or None for the plain sum) and the sum of the streams
+    into `total` float32 [T, H]; every part optional."""
+    _need(streams, torch.float32, "streams", 3)
+    T, S, H = streams.shape
+    for t, n in ((single, "single"), (total, "total")):
+        if t is not None:
+            _need(t, torch.float32, n, 2)
+            if t.shape != (T, H):
+                raise KernelError(f"hc_step: {n} must be [{T}, {H}]")
+    dt = None
+    for t, n in ((y, "y"), (h, "h")):
+        if t is not None:
+            _need(t, None, n, 2)
+            if t.shape != (T, H) or (dt is not None and t.dtype != dt):
+                raise KernelError(f"hc_step: {n} must be [{T}, {H}] in one dtype")
+            dt = t.dtype
+    for t, n, shape in ((mix, "mix", (S, S)), (out_w, "out_w", (S,)), (in_w, "in_w", (S,))):
+        if t is not None:
+            _need(t, torch.float32, n)
+            if tuple(t.shape) != shape:
+                raise KernelError(f"hc_step: {n} must be {shape}")
+    if (y is None) != (mix is None) or (y is None) != (out_w is None) or (in_w is None) != (h is None):
+        raise KernelError("hc_step: y comes with mix and out_w, in_w with h")
+    alpha = w = b = None
+    if norm is not None:
+        alpha, w, b = norm
+        _need(alpha, torch.float32, "alpha"); _need(w, torch.float32, "weight", 1); _need(b, torch.float32, "bias", 1)
+        if alpha.numel() != 1 or w.shape[0] != H or b.shape[0] != H:
+            raise KernelError("hc_step: the norm's alpha is one number, its weight and bias have H entries")
+    _check(_fn("hyper", "vl_hc_step")(_ptr(streams), _ptr(single), _ptr(y), dtype_code(dt or torch.float32), _ptr(mix),
+                                      _ptr(out_w), _ptr(in_w), _ptr(alpha), _ptr(w), _ptr(b), _ptr(h), _ptr(total),
+                                      T, S, H, _stream()), "vl_hc_step")
+
+
+def dyt_rows(x, delta, rows, alpha, weight, bias, out):
+    """out[r] = tanh(alpha * x[row r]) * weight + bias; x float32 [T, H] (+= delta first; stored when rows is None)."""
+    _need(x, torch.float32, "x", 2); _need(out, None, "out", 2)
+    _need(alpha, torch.float32, "alpha"); _need(weight, torch.float32, "weight", 1); _need(bias, torch.float32, "bias", 1)
+    H = x.shape[1]
+    R = x.shape[0] if rows is None else rows.shape[0]
+    if alpha.numel() != 1 or weight.shape[0] != H or bias.shape[0] != H or out.shape != (R, H):
+        raise KernelError("dyt_rows: shapes disagree")
+    if delta is not None:
+        _need(delta, out.dtype, "delta", 2)
+        if delta.shape != x.shape:
+            raise KernelError("dyt_rows: delta must match x")
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+    _check(_fn("hyper", "vl_dyt_rows")(_ptr(x), _ptr(delta), _ptr(rows), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out),
+                                       dtype_code(out.dtype), R, H, _stream()), "vl_dyt_rows")
+    return out
+
+
+# ---------------------------------------------------------------- recurrent mixers (csrc/recurrent.cu)
+RC_THREADS, RC_ROWS = 128, 16
+
+
+def scan_lanes(n: int) -> int:
+    """Lanes that share one column of a state with n rows (what the scan kernels pick)."""
+    L = 1
+    while L * RC_ROWS < n:
+        L *= 2
+    if L > 32:
+        raise KernelError(f"the scan kernels take states of up to {32 * RC_ROWS} rows, got {n}")
+    return L
+
+
+def scan_column_tiles(n: int, columns: int) -> int:
+    ct = RC_THREADS // scan_lanes(n)
+    return -(-columns // ct)
+
+
+def mlstm_state_floats(H, D, P) -> int:
+    """S [H, D, P], then a normaliser [D] and a running maximum for every tile of columns of every head."""
+    Z = scan_column_tiles(D, P)
+    return H * D * P + H * Z * D + H * Z
+
+
+def _state_args(state, state_off, need):
+    _need(state, torch.float32, "state", 2)
+    if state_off < 0 or state_off + need > state.shape[1]:
+        raise KernelError(f"a state row of {state.shape[1]} floats cannot hold {need} at {state_off}")
+    return state.data_ptr() + 4 * state_off, state.shape[1]
+
+
+def _seg_args(cu, slots):
+    _need(cu, torch.int32, "cu_seqlens", 1); _need(slots, torch.int32, "state_slots", 1)
+    B = cu.shape[0] - 1
+    if slots.shape[0] < B:
+        raise KernelError("one state slot per request")
+    return B
+
+
+def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=True):
+    """out float32 [T, C] = act(causal convolution over time of columns col0 .. col0+C of x [T, ld]); weight float32
+    [C, taps]; the last taps-1 inputs live at `state_off` of every request's state row [(taps-1), C]."""
+    _need(x, None, "x", 2); _need(weight, torch.float32, "weight", 2); _need(out, torch.float32, "out", 2)
+    taps = weight.shape[1]
+    if weight.shape[0] != C or out.shape != (x.shape[0], C):
+        raise KernelError("short_conv: shapes disagree")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+    B = _seg_args(cu, slots)
+    sp, stride = _state_args(state, state_off, (taps - 1) * C)
+    _check(_fn("recurrent", "vl_short_conv")(_ptr(x), dtype_code(x.dtype), x.shape[1], col0, C, _ptr(weight), _ptr(bias), taps,
+                                             sp, stride, _ptr(cu), _ptr(slots), B, _ptr(out), int(bool(act)), _stream()),
+           "vl_short_conv")
+    return out
+
+
+def ssd_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, state_off, cu, slots, y, H, G, N, P):
+    _need(xbc, torch.float32, "xbc", 2); _need(proj, None, "proj", 2); _need(y, torch.float32, "y", 2)
+    for t, n in ((dt_bias, "dt_bias"), (A_log, "A_log"), (D, "D")):
+        _need(t, torch.float32, n, 1)
+        if t.shape[0] != H:
+            raise KernelError(f"ssd_scan: {n} has one entry per head")
+    T = xbc.shape[0]
+    if proj.shape[0] != T or y.shape != (T, H * P) or dt_col + H > proj.shape[1]:
+        raise KernelError("ssd_scan: shapes disagree")
+    B = _seg_args(cu, slots)
+    sp, stride = _state_args(state, state_off, H * N * P)
+    scan_lanes(N)
+    _check(_fn("recurrent", "vl_ssd_scan")(_ptr(xbc), xbc.shape[1], _ptr(proj), dtype_code(proj.dtype), proj.shape[1], dt_col,
+                                           _ptr(dt_bias), _ptr(A_log), _ptr(D), sp, stride, _ptr(cu), _ptr(slots), B, _ptr(y),
+                                           H, G, N, P, _stream()), "vl_ssd_scan")
+    return y
+
+
+def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, q_scale, denom_eps, state, state_off, cu, slots, o, H, D, P):
+    _need(proj, None, "proj", 2); _need(o, torch.float32, "o", 2)
+    _need(i_bias, torch.float32, "i_bias", 1); _need(f_bias, torch.float32, "f_bias", 1)
+    T, ld = proj.shape
+    if o.shape != (T, H * P) or i_bias.shape[0] != H or f_bias.shape[0] != H:
+        raise KernelError("mlstm_scan: shapes disagree")
+    if max(q_col + H * D, k_col + H * D, v_col + H * P, i_col + H, f_col + H) > ld:
+        raise KernelError("mlstm_scan: a column range leaves the rows")
+    B = _seg_args(cu, slots)
+    sp, stride = _state_args(state, state_off, mlstm_state_floats(H, D, P))
+    _check(_fn("recurrent", "vl_mlstm_scan")(_ptr(proj), dtype_code(proj.dtype), ld, q_col, k_col, v_col, i_col, f_col,
+                                             _ptr(i_bias), _ptr(f_bias), float(cap), float(q_scale), float(denom_eps), sp, stride, _ptr(cu),
+                                             _ptr(slots), B, _ptr(o), H, D, P, _stream()), "vl_mlstm_scan")
+    return o
+
+
+def delta_scan(qkv, decay, decay_col, dt_bias, A_log, proj, beta_col, q_scale, unit_eps, state, state_off, cu, slots, o, H, G, D, P):
+    _need(qkv, torch.float32, "qkv", 2); _need(decay, None, "decay", 2); _need(proj, decay.dtype, "proj", 2)
+    _need(o, torch.float32, "o", 2); _need(dt_bias, torch.float32, "dt_bias", 1); _need(A_log, torch.float32, "A_log", 1)
+    T = qkv.shape[0]
+    if decay.shape[0] != T or decay_col + H * D > decay.shape[1] or proj.shape[0] != T or o.shape != (T, H * P) or dt_bias.shape[0] != H * D \
+            or A_log.shape[0] != H or beta_col + H > proj.shape[1]:
+        raise KernelError("delta_scan: shapes disagree")
+    B = _seg_args(cu, slots)
+    sp, stride = _state_args(state, state_off, H * D * P)
+    scan_lanes(D)
+    _check(_fn("recurrent", "vl_delta_scan")(_ptr(qkv), qkv.shape[1], _ptr(decay), decay.shape[1], decay_col, _ptr(dt_bias), _ptr(A_log), _ptr(proj),
+                                             dtype_code(proj.dtype), proj.shape[1], beta_col, float(q_scale), float(unit_eps),
+                                             sp, stride, _ptr(cu), _ptr(slots), B, _ptr(o), H, G, D, P, _stream()),
+           "vl_delta_scan")
+    return o
+
+
+GATES = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def gate_norm(y, gate, gate_col, gate_kind, gate_first, weight, eps, out, part):
+    """out [T, W] = RMS norm of y float32 [T, W] over parts of `part` columns, times weight (W entries, or `part`
+    entries shared by the parts), with a gate taken from columns gate_col .. of `gate`: out = rms(y * g) * w when
+    gate_first, else rms(y) * w * g; g = silu or sigmoid of the gate's value."""
+    _need(y, torch.float32, "y", 2); _need(out, None, "out", 2); _need(weight, torch.float32, "weight", 1)
+    T, W = y.shape
+    if out.shape != (T, W) or weight.shape[0] not in (W, part):
+        raise KernelError("gate_norm: shapes disagree")
+    ld = 0
+    if gate is not None:
+        _need(gate, out.dtype, "gate", 2)
+        ld = gate.shape[1]
+        if gate.shape[0] != T or gate_col + W > ld:
+            raise KernelError("gate_norm: the gate's columns leave its rows")
+    _check(_fn("recurrent", "vl_gate_norm")(_ptr(y), _ptr(gate), dtype_code(out.dtype), ld, gate_col, GATES[gate_kind if gate is not None else None],
+                                            int(bool(gate_first)), _ptr(weight), weight.shape[0], float(eps), _ptr(out), T, W,
+                                            part, _stream()), "vl_gate_norm")
+    return out

@@ -23,10 +23,28 @@ def parse_dtype(dtype):
         raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
 
 
+def tensor_shapes(model_dir) -> dict:
+    """{tensor name: shape} from the headers of a folder's weight files (no data is read); {} when there are none."""
+    from ..weights.loader import WeightError, find_weight_files
+    from ..weights.safetensors_io import SafetensorsError, SafetensorsFile
+    shapes = {}
+    try:
+        for path in find_weight_files(model_dir):
+            f = SafetensorsFile(path)
+            try:
+                for name in f.names():
+                    shapes[name] = tuple(f.info(name)[1])
+            finally:
+                f.close()
+    except (OSError, WeightError, SafetensorsError):
+        return {}
+    return shapes
+
+
 def load_model_dir(model_dir, dtype, device):
     """(typed configuration, plan, {name: device tensor})."""
     dtype = parse_dtype(dtype)
-    cfg, plan = plan_from_config_json(read_config_json(model_dir))
+    cfg, plan = plan_from_config_json(read_config_json(model_dir), shapes=tensor_shapes(model_dir))
     weights = load_weights(model_dir, declare_model(plan), dtype, device, unused=plan.unused_tensors)
     return cfg, plan, weights
 

@@ -35,22 +35,42 @@ def check_attention_sizes(spec: AttentionSpec):
         raise ValueError(f"window {spec.window} must be positive (None reads every earlier key)")
 
 
+def _pad_heads(w, heads, size, padded):
+    """Rows (or entries) of `heads` heads of `size` each, every head padded with zeros to `padded`."""
+    if size == padded:
+        return w
+    shape = (heads, size) + tuple(w.shape[1:])
+    out = torch.zeros((heads, padded) + tuple(w.shape[1:]), dtype=w.dtype, device=w.device)
+    out[:, :size] = w.reshape(shape)
+    return out.reshape((heads * padded,) + tuple(w.shape[1:]))
+
+
+def _pair_order(head_dim, rotary_dim, device):
+    """The order of a head's features that puts neighbours (2i, 2i+1) of the first rotary_dim features at (i, i + rotary_dim/2):
+    q.k does not change when q and k are permuted alike, so an interleaved rotation is the rotate-half one on permuted heads."""
+    idx = torch.arange(head_dim, device=device)
+    idx[:rotary_dim] = torch.cat([torch.arange(0, rotary_dim, 2, device=device), torch.arange(1, rotary_dim, 2, device=device)])
+    return idx
+
+
 @MIXERS.register("gqa_attention")
 class GqaAttention:
     graph_safe = True          # launches only stream-ordered kernels: a step can be captured in a CUDA graph
 
     @staticmethod
     def declare(spec: AttentionSpec) -> dict:
-        qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
-        d = {"q_proj.weight": TensorDecl((qd, spec.hidden_size)),
-             "k_proj.weight": TensorDecl((kvd, spec.hidden_size)),
-             "v_proj.weight": TensorDecl((kvd, spec.hidden_size)),
-             "o_proj.weight": TensorDecl((spec.hidden_size, qd))}
+        vd = spec.v_head_dim or spec.head_dim
+        qd, kd, vdim = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.num_kv_heads * vd
+        q, k, v, o = spec.names
+        qb, kb, vb, ob = spec.bias_names
+        d = {q: TensorDecl((qd, spec.hidden_size)), k: TensorDecl((kd, spec.hidden_size)),
+             v: TensorDecl((vdim, spec.hidden_size)), o: TensorDecl((spec.hidden_size, spec.num_heads * vd))}
         if spec.bias:
-            d.update({"q_proj.bias": TensorDecl((qd,)), "k_proj.bias": TensorDecl((kvd,)),
-                      "v_proj.bias": TensorDecl((kvd,))})
+            d.update({qb: TensorDecl((qd,)), kb: TensorDecl((kd,)), vb: TensorDecl((vdim,))})
+        if spec.out_bias:
+            d[ob] = TensorDecl((spec.hidden_size,))
         if spec.qk_norm is not None:
-            for side in ("q_norm.", "k_norm."):
+            for side in spec.norm_prefixes:
                 for name, decl in NORMS.get(spec.qk_norm.kind).declare(spec.qk_norm).items():
                     d[side + name] = decl
         if spec.position is not None:
@@ -59,20 +79,49 @@ class GqaAttention:
         return d
 
     @staticmethod
+    def padded_head_dim(spec: AttentionSpec) -> int:
+        """The head size the kernels see: key and value heads of one size, a multiple of 16.  Heads of other sizes are
+        padded with zero features when the weights are bound (zero rows of q, k, v, zero columns of o), which changes no
+        score and no output; the head norm's mean then runs over the padded size and is set right by its weight and eps."""
+        return -(-max(spec.head_dim, spec.v_head_dim or spec.head_dim) // 16) * 16
+
+    @staticmethod
     def cache_need(spec: AttentionSpec):
-        return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window)
+        return PagedKV(spec.num_kv_heads, GqaAttention.padded_head_dim(spec), spec.window)
 
     def __init__(self, spec: AttentionSpec, weights: dict, ctx):
+        import dataclasses
+        hd, vd, pd = spec.head_dim, spec.v_head_dim or spec.head_dim, self.padded_head_dim(spec)
+        self.true_spec = spec
+        # what the kernels see: heads of the padded size (scale and window as given)
+        spec = dataclasses.replace(spec, head_dim=pd, v_head_dim=None,
+                                   scale=spec.scale if spec.scale is not None else hd ** -0.5,
+                                   qk_norm=None if spec.qk_norm is None else dataclasses.replace(spec.qk_norm, size=pd))
         check_attention_sizes(spec)
         self.spec = spec
         self.dtype = ctx.dtype
-        qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0)
+        nq, nkv = spec.num_heads, spec.num_kv_heads
+        qn, kn, vn, on = spec.names
+        wq, wk, wv, wo = weights[qn], weights[kn], weights[vn], weights[on]
+        biases = [weights[n].float() for n in spec.bias_names[:3]] if spec.bias else None
+        order = None
+        rot = self.true_spec.position
+        if rot is not None and getattr(rot, "interleaved", False):
+            order = _pair_order(hd, rot.dim, wq.device)
+            wq = wq.reshape(nq, hd, -1)[:, order].reshape(nq * hd, -1)
+            wk = wk.reshape(nkv, hd, -1)[:, order].reshape(nkv * hd, -1)
+            if biases is not None:
+                biases[0] = biases[0].reshape(nq, hd)[:, order].reshape(-1)
+                biases[1] = biases[1].reshape(nkv, hd)[:, order].reshape(-1)
+        wq, wk, wv = _pad_heads(wq, nq, hd, pd), _pad_heads(wk, nkv, hd, pd), _pad_heads(wv, nkv, vd, pd)
+        if vd != pd:
+            wo = _pad_heads(wo.t().contiguous(), nq, vd, pd).t().contiguous()
         bias = None
-        if spec.bias:
-            bias = torch.cat([weights["q_proj.bias"].float(), weights["k_proj.bias"].float(),
-                              weights["v_proj.bias"].float()], dim=0)
-        self.qkv_proj = Linear(qkv.contiguous(), bias)
-        self.o_proj = Linear(weights["o_proj.weight"])
+        if biases is not None:
+            bias = torch.cat([_pad_heads(biases[0], nq, hd, pd), _pad_heads(biases[1], nkv, hd, pd),
+                              _pad_heads(biases[2], nkv, vd, pd)], dim=0)
+        self.qkv_proj = Linear(torch.cat([wq, wk, wv], dim=0).contiguous(), bias)
+        self.o_proj = Linear(wo.contiguous(), weights[spec.bias_names[3]].float() if spec.out_bias else None)
         self.q_norm = self.k_norm = None
         # The kernel that rotates and writes the cache also applies an RMS norm to every head.  A head norm
         # that says it is one (`fused_rms()` -> (weight, eps)) runs there; any other kind must change the
@@ -80,18 +129,34 @@ class GqaAttention:
         self.fused_head_norm = None
         if spec.qk_norm is not None:
             cls = NORMS.get(spec.qk_norm.kind)
-            self.q_norm = cls(spec.qk_norm, sub_weights(weights, "q_norm."), ctx)
-            self.k_norm = cls(spec.qk_norm, sub_weights(weights, "k_norm."), ctx)
+            true_norm = self.true_spec.qk_norm
+            norms = []
+            for side in spec.norm_prefixes:
+                nw = dict(sub_weights(weights, side))
+                if order is not None or pd != hd:
+                    # the norm's weights follow their features; over a padded head sum(x^2) / pd stands for sum(x^2) / hd:
+                    # x / sqrt(ss/hd + eps) = x sqrt(hd/pd) / sqrt(ss/pd + eps hd/pd)
+                    for name, decl in cls.declare(true_norm).items():
+                        if tuple(decl.shape) == (hd,):
+                            w = nw[name].float()
+                            w = w[order] if order is not None else w
+                            nw[name] = _pad_heads(w * (hd / pd) ** 0.5, 1, hd, pd)
+                norms.append(cls(dataclasses.replace(spec.qk_norm, eps=spec.qk_norm.eps * hd / pd), nw, ctx))
+            self.q_norm, self.k_norm = norms
             if hasattr(self.q_norm, "fused_rms"):
                 (qw, eps), (kw, _) = self.q_norm.fused_rms(), self.k_norm.fused_rms()
                 self.fused_head_norm = (qw, kw, eps)
+            elif pd != hd:
+                raise TypeError(f"norm kind {spec.qk_norm.kind!r} cannot norm heads that are padded from {hd} to {pd} features")
             elif not hasattr(self.q_norm, "apply_heads"):
                 raise TypeError(f"norm kind {spec.qk_norm.kind!r} cannot serve as a head norm: it offers neither "
                                 f"fused_rms() nor apply_heads(qkv, first_head, num_heads, head_dim, step)")
         self.position = None
         if spec.position is not None:
-            self.position = POSITIONS.get(spec.position.kind)(spec.position, sub_weights(weights, "rotary."), ctx)
-        self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
+            pos = dataclasses.replace(spec.position, head_dim=pd, rotary_dim=spec.position.dim, interleaved=False) \
+                if hasattr(spec.position, "rotary_dim") else spec.position
+            self.position = POSITIONS.get(pos.kind)(pos, sub_weights(weights, "rotary."), ctx)
+        self.scale = spec.scale
 
     def factors_norms(self, M) -> bool:
         """For M rows: the input may come as `ScaledRows` and the result may go `into_stream`."""

@@ -126,6 +126,7 @@ class CallCache:
     v: Optional[torch.Tensor] = None
     writes: bool = True
     state: Optional[torch.Tensor] = None
+    parts: Optional[list] = None              # a call with several needs (cache.spec.Several): one CallCache per need
 
 
 @dataclass
@@ -135,6 +136,14 @@ class Residual:
     normed: Optional["ScaledRows"] = None     # output of the norm `normed_for` on x, in factored form
     normed_for: object = None
     cast: Optional[torch.Tensor] = None       # x in the activation dtype, when the kernel that last wrote x left it
+    streams: Optional[torch.Tensor] = None    # float32 [T, S, H]: the copies of the stream that hyper-connection blocks keep
+    deferred: object = None                   # a write-back that the last block left undone: deferred(next_read) does it,
+                                              # together with the read that a following block of the same kind asks for
+
+    def settle(self):
+        """Bring `x` up to date (blocks that keep several streams write back lazily)."""
+        if self.deferred is not None:
+            self.deferred(None)
 
 
 @dataclass

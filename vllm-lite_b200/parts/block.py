@@ -143,3 +143,120 @@ def _exact(weights, prefix, norm_spec):
     if getattr(norm_spec, "tensor", "weight") == "":
         return {"": weights[prefix]} if prefix in weights else {}
     return sub_weights(weights, prefix)
+
+
+@BLOCKS.register("hyper_connection")
+class HyperConnectionBlock:
+    """A block over several copies x_1 .. x_S of the stream (float32 [T, S, H], made of S copies of the single stream
+    by the first such block).  Sub-layer q with the learned in_q [S], out_q [S], mix_q [S, S] (indexed [from, to]):
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t at once)
+
+    and the single stream is the sum of the copies.  A write-back and the read that follows it are one pass over the
+    streams (`ops.hc_step`), also across blocks: the last write-back of a block is left to the next block of this kind
+    (`Residual.deferred`), or to the model's end, which also asks for the sum."""
+
+    takes_deferred = True
+
+    @staticmethod
+    def declare(spec: BlockSpec) -> dict:
+        norm1, mixer, norm2, ffn = spec.names
+        d = {}
+        d.update(prefixed(NORMS.get(spec.norm1.kind).declare(spec.norm1), norm1))
+        d.update(prefixed(MIXERS.get(spec.mixer.kind).declare(spec.mixer), mixer))
+        subs = [0]
+        if spec.ffn is not None:
+            d.update(prefixed(NORMS.get(spec.norm2.kind).declare(spec.norm2), norm2))
+            d.update(prefixed(FEED_FORWARDS.get(spec.ffn.kind).declare(spec.ffn), ffn))
+            subs.append(1)
+        from .spec import TensorDecl
+        for q in subs:
+            hc, S = spec.hyper[q], spec.hyper[q].streams
+            a, o, m = hc.names
+            p = spec.hyper_prefixes[q]
+            d.update({p + a: TensorDecl((S,), init="norm"), p + o: TensorDecl((S,), init="norm"),
+                      p + m: TensorDecl((S, S), init="identity")})
+        return d
+
+    @staticmethod
+    def cache_need(spec: BlockSpec):
+        return MIXERS.get(spec.mixer.kind).cache_need(spec.mixer)
+
+    def __init__(self, spec: BlockSpec, weights: dict, ctx):
+        from ..csrc import ops
+        self.spec = spec
+        self.dtype = ctx.dtype
+        self.streams = int(spec.streams)
+        if not 1 <= self.streams <= ops.HC_MAX_STREAMS:
+            raise ValueError(f"a hyper-connection block keeps 1 to {ops.HC_MAX_STREAMS} streams, got {self.streams}")
+        norm1, mixer, norm2, ffn = spec.names
+        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, sub_weights(weights, norm1), ctx)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, mixer), ctx)
+        self.norm2 = self.ffn = None
+        if spec.ffn is not None:
+            self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, sub_weights(weights, norm2), ctx)
+            self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, ffn), ctx)
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.hc = []
+        for q in range(2 if spec.ffn is not None else 1):
+            a, o, m = spec.hyper[q].names
+            p = spec.hyper_prefixes[q]
+            self.hc.append((f32(weights[p + a]), f32(weights[p + o]), f32(weights[p + m])))
+        self.graph_safe = bool(getattr(self.mixer, "graph_safe", False)
+                               and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    def _read(self, residual, step, q, pending):
+        """h for sub-layer q, after the write-back `pending` = (y, mix, out) of the sub-layer before (or None)."""
+        from ..csrc import ops
+        norm = self.norm1 if q == 0 else self.norm2
+        in_w = self.hc[q][0]
+        T, H = residual.x.shape
+        single = None
+        if residual.streams is None or residual.streams.shape != (T, self.streams, H):
+            if pending is not None:
+                raise RuntimeError("a write-back is pending for streams that do not exist")
+            residual.streams = step.workspace.get(step.tag + "streams", (T, self.streams, H), torch.float32)
+            single = residual.x
+        h = step.workspace.get(step.tag + f"hc.h{q}", (T, H), self.dtype)
+        y, mix, out_w = pending if pending is not None else (None, None, None)
+        fused = getattr(norm, "elementwise", None)
+        if fused is not None:
+            ops.hc_step(residual.streams, single=single, y=y, mix=mix, out_w=out_w, in_w=in_w, norm=fused(), h=h)
+            return h
+        # a norm of another kind reads the plain sum u through its own kernel
+        u = step.workspace.get(step.tag + "hc.u", (T, H), torch.float32)
+        ops.hc_step(residual.streams, single=single, y=y, mix=mix, out_w=out_w, in_w=in_w, h=u)
+        return norm(u, None, step, tag=f"hc.norm{q}")
+
+    def __call__(self, residual, step, cache):
+        from ..csrc import ops
+        if residual.pending is not None or residual.normed is not None:
+            raise NotImplementedError("a hyper-connection block after a block that leaves its result pending")
+        pending = None
+        if residual.deferred is not None:
+            pending, residual.deferred = residual.deferred.pending, None
+        h = self._read(residual, step, 0, pending)
+        y = self.mixer(h, step, cache)
+        last = (y, self.hc[0][2], self.hc[0][1])
+        if self.ffn is not None:
+            h = self._read(residual, step, 1, last)
+            y = self.ffn(h, step)
+            last = (y, self.hc[1][2], self.hc[1][1])
+        residual.cast = None
+        residual.deferred = _DeferredWriteBack(residual, last)
+
+
+class _DeferredWriteBack:
+    """The last write-back of a hyper-connection block, not yet done.  The next block of the kind takes `pending`
+    and does it in its first pass; called (by `Residual.settle`) it is done alone, and the single stream x
+    becomes the sum of the copies."""
+
+    def __init__(self, residual, pending):
+        self.residual, self.pending = residual, pending
+
+    def __call__(self, _next=None):
+        from ..csrc import ops
+        r = self.residual
+        y, mix, out_w = self.pending
+        ops.hc_step(r.streams, y=y, mix=mix, out_w=out_w, total=r.x)
+        r.deferred = None

@@ -46,6 +46,10 @@ class RoutedExperts:
         from ..csrc import ops
         if not 0 < spec.top <= spec.num_experts:
             raise ValueError(f"routed experts: top {spec.top} of {spec.num_experts} experts")
+        if spec.groups < 1 or spec.num_experts % spec.groups or not 1 <= spec.keep_groups <= spec.groups \
+                or spec.keep_groups * (spec.num_experts // spec.groups) < spec.top:
+            raise ValueError(f"routed experts: {spec.num_experts} experts in {spec.groups} groups of which {spec.keep_groups} "
+                             f"are kept cannot offer {spec.top} choices")
         if spec.activation not in ops.ACTIVATIONS or spec.score not in ops.ROUTER_SCORES:
             raise ValueError(f"routed experts: activation {spec.activation!r} / score {spec.score!r} not known")
         self.spec = spec
@@ -86,7 +90,7 @@ class RoutedExperts:
         tile_group = ws.get(tag + "moe.tiles", (cap // bm,), torch.int32)
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
         logits = ws.get(tag + "moe.logits", (ops.router_slices(H), T, E), torch.float32)
-        ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize)
+        ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize, s.groups, s.keep_groups)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
         act = ws.get(tag + "moe.act", (cap, I), self.dtype)
         if big:

@@ -1,5 +1,6 @@
 """Gated feed-forward with a choice of activation and optional biases:
-down(act(gate(h) + b_g) * (up(h) + b_u)) + b_d, act = "silu" or "relu".
+down(f(gate(h) + b_g, up(h) + b_u)) + b_d, f(g, u) = silu(g) u, relu(g) u, or the capped swish
+g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
 
 gate and up are stacked into one matrix (gate rows, then up rows) so that one product serves both;
 the activation is one kernel on the stacked result and adds the two projections' biases on the way (float32);
@@ -31,9 +32,8 @@ class GatedMlp:
 
     def __init__(self, spec: GatedMlpSpec, weights: dict, ctx):
         from ..csrc import ops
-        if spec.activation not in ("silu", "relu"):
-            raise ValueError(f"gated_mlp: activation {spec.activation!r}; known: silu, relu")
-        assert spec.activation in ops.ACTIVATIONS
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation {spec.activation!r}; known: {', '.join(ops.ACTIVATIONS)}")
         self.spec = spec
         self.dtype = ctx.dtype
         gate, up, down = spec.names
@@ -48,5 +48,6 @@ class GatedMlp:
         from ..csrc import ops
         gu = self.gate_up(h, step, "mlp.gate_up")
         act = step.workspace.get(step.tag + "mlp.act", (gu.shape[0], self.spec.intermediate_size), gu.dtype)
-        ops.gated_act(gu, act, self.spec.activation, bias=self.gate_up_bias)
+        s = self.spec
+        ops.gated_act(gu, act, s.activation, 0, s.alpha, s.limit, s.up_shift, bias=self.gate_up_bias)
         return self.down(act, step, "mlp.down")

@@ -46,8 +46,9 @@ class CausalLM:
         self.head = HEADS.get(head.kind)(head, sub_weights(weights, plan.head_prefix), ctx, embedding=self.embedding)
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in [self.embedding, self.head] + self.layers)
 
-    def forward(self, step, caches) -> torch.Tensor:
-        """Logits float32 [len(step.logit_rows), vocab]."""
+    def forward(self, step, caches, watch=None) -> torch.Tensor:
+        """Logits float32 [len(step.logit_rows), vocab].  `watch(i, x)`, when given, is called after every entry of
+        the running order with the stream brought up to date (a reader for tests and comparisons)."""
         ws = step.workspace
         x = ws.get(step.tag + "residual", (step.num_tokens, self.plan.hidden_size), torch.float32)
         self.embedding(step, x)
@@ -55,6 +56,8 @@ class CausalLM:
         order = self.plan.order
         for i, (call, cache) in enumerate(zip(order, caches)):
             layer = self.layers[call.layer]
+            if residual.deferred is not None and not getattr(layer, "takes_deferred", False):
+                residual.settle()
             if getattr(layer, "chains_norms", False):
                 # a block may leave the next block's first norm in factored form (parts/base.py, ScaledRows)
                 nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
@@ -62,6 +65,12 @@ class CausalLM:
                 layer(residual, step, cache, next_norm=ask(step.num_tokens) if ask else None)
             else:
                 layer(residual, step, cache)
+            if watch is not None:
+                if residual.pending is not None or residual.normed is not None:
+                    raise NotImplementedError("watching a model whose blocks leave their results pending")
+                residual.settle()
+                watch(i, residual.x)
+        residual.settle()
         R = step.logit_rows.shape[0]
         if R == 0:
             return ws.get(step.tag + "logits", (0, self.plan.vocab_size), torch.float32)

@@ -63,3 +63,33 @@ class LayerNorm:
         R = x.shape[0] if rows is None else rows.shape[0]
         out = step.workspace.get(step.tag + tag, (R, self.spec.size), self.dtype)
         return ops.layernorm_rows(x, rows, self.weight, self.spec.eps, out)
+
+
+@NORMS.register("dyn_tanh")
+class DynTanh:
+    """h = tanh(alpha x) * w + b, element by element in float32: alpha a learned scalar, w and b vectors; no mean and
+    no variance are computed, so the spec's eps is not used.  A block that keeps several streams applies it inside
+    its own pass over the streams (`elementwise()` hands it the three tensors)."""
+
+    @staticmethod
+    def declare(spec: NormSpec) -> dict:
+        return {spec.tensor: TensorDecl((spec.size,), init="norm"),
+                spec.tensor + spec.bias_suffix: TensorDecl((spec.size,)),
+                spec.tensor + spec.alpha_suffix: TensorDecl((), init="norm")}
+
+    def __init__(self, spec: NormSpec, weights: dict, ctx):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.weight = f32(weights[spec.tensor])
+        self.bias = f32(weights[spec.tensor + spec.bias_suffix])
+        self.alpha = f32(weights[spec.tensor + spec.alpha_suffix]).reshape(1)
+
+    def elementwise(self):
+        return self.alpha, self.weight, self.bias
+
+    def __call__(self, x, delta, step, rows=None, tag="norm"):
+        from ..csrc import ops
+        R = x.shape[0] if rows is None else rows.shape[0]
+        out = step.workspace.get(step.tag + tag, (R, self.spec.size), self.dtype)
+        return ops.dyt_rows(x, delta, rows, self.alpha, self.weight, self.bias, out)

@@ -22,7 +22,8 @@ class TensorDecl:
     """One tensor that a part binds by name.
 
     `init` names the distribution of the random-weights mode: "linear"
-    (N(0, std)), "norm" (1 + N(0, norm_std)).  `store` is the dtype the tensor
+    (N(0, std)), "norm" (1 + N(0, norm_std)), "identity" (a square matrix: I + N(0, norm_std)), "conv" / "unit" (N(0, 0.5): taps of a short convolution, biases and
+    logarithms of gates and decays).  `store` is the dtype the tensor
     has in a written folder and the least precision it is kept in:
     "model" (the model dtype, bfloat16 on disk) or "float32".
     """
@@ -33,22 +34,28 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class NormSpec:
-    """`kind`: "rms_norm" (x / sqrt(mean x^2 + eps) * w) or "layer_norm" ((x - mean) / sqrt(var + eps) * w,
-    no bias).  `tensor`: the weight's name relative to the norm's prefix ("" when the prefix is the whole name)."""
+    """`kind`: "rms_norm" (x / sqrt(mean x^2 + eps) * w), "layer_norm" ((x - mean) / sqrt(var + eps) * w,
+    no bias) or "dyn_tanh" (tanh(alpha x) * w + b, alpha a learned scalar: no mean, no variance, eps unused).
+    `tensor`: the weight's name relative to the norm's prefix ("" when the prefix is the whole name); a norm with
+    a bias vector or a scalar stores them as `tensor + bias_suffix` / `tensor + alpha_suffix`."""
     size: int
     eps: float
     kind: str = "rms_norm"
     tensor: str = "weight"
+    bias_suffix: str = ".b"
+    alpha_suffix: str = ".alpha"
 
 
 @dataclass(frozen=True)
 class RotarySpec:
-    """Rotate-half rotary position encoding of the first `rotary_dim` features
-    of each head; inv_freq[i] = theta^(-2i / rotary_dim)."""
+    """Rotary position encoding of the first `rotary_dim` features of each head; inv_freq[i] =
+    theta^(-2i / rotary_dim).  Feature i turns with feature i + rotary_dim/2 (rotate-half), or, when
+    `interleaved`, feature 2i with feature 2i+1."""
     head_dim: int
     theta: float
     rotary_dim: Optional[int] = None
     kind: str = "rotary"
+    interleaved: bool = False
 
     @property
     def dim(self) -> int:
@@ -72,8 +79,15 @@ class AttentionSpec:
     position: Optional[RotarySpec] = None
     window: Optional[int] = None
     scale: Optional[float] = None
-    bias: bool = False              # q/k/v projections with a bias vector each (the output projection has none)
+    bias: bool = False              # q/k/v projections with a bias vector each
     kind: str = "gqa_attention"
+    out_bias: bool = False          # the output projection has a bias vector too
+    v_head_dim: Optional[int] = None    # size of a value head when it differs from head_dim
+    # tensor names relative to the mixer's prefix: q, k, v, o weights; the suffix of a projection's bias; the
+    # prefixes of the two head norms
+    names: Tuple[str, str, str, str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")
+    bias_names: Tuple[str, str, str, str] = ("q_proj.bias", "k_proj.bias", "v_proj.bias", "o_proj.bias")
+    norm_prefixes: Tuple[str, str] = ("q_norm.", "k_norm.")
 
 
 @dataclass(frozen=True)
@@ -132,12 +146,16 @@ class LatentAttentionSpec:
 
 @dataclass(frozen=True)
 class GatedMlpSpec:
-    """down(act(gate(h)) * up(h)) with a choice of activation ("silu", "relu") and optional bias vectors on all
+    """down(act(gate(h)) * up(h)) with a choice of activation ("silu", "relu", or "capped_swish": g' = min(g, limit),
+    u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + up_shift)) and optional bias vectors on all
     three projections.  `names`: (gate, up, down) relative to the part's prefix; a bias is `<name><bias_suffix>`."""
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
     bias: bool = False
+    alpha: float = 1.0
+    limit: float = 0.0
+    up_shift: float = 0.0
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
     bias_suffix: str = ".b"
     kind: str = "gated_mlp"
@@ -164,10 +182,97 @@ class RoutedExpertsSpec:
     score: str = "sigmoid"
     renormalize: bool = False
     scale_input: bool = True
+    # experts in `groups` equal groups of neighbours; a group's score is its largest score and only experts of
+    # the `keep_groups` best groups can be chosen (1, 1: no grouping)
+    groups: int = 1
+    keep_groups: int = 1
     router: str = "router"
     expert_prefix: str = "e{}."
     names: Tuple[str, str, str] = ("gate", "up", "down")
     kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """Selective state space with one scalar decay per head (state-space duality form).
+
+    W_in h = [z: inner | x: inner | B: groups*state | C: groups*state | dt: heads], inner = heads * vdim; x, B, C pass a
+    causal convolution of `conv` taps per channel (with bias) and silu; dt = softplus(dt + dt_bias);
+    S <- exp(-exp(A_log) dt) S + dt B x^T (state x vdim per head, heads share B, C in groups), y = S^T C + D x;
+    out = W_o (rms_parts(y * silu(z)) * norm), the RMS norm over `norm_groups` equal parts.
+    `names`: (in, conv, conv bias, dt_bias, A_log, D, norm, o)."""
+    hidden_size: int
+    num_heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+    eps: float
+    names: Tuple[str, ...] = ("in", "conv", "conv.b", "dt_bias", "A_log", "D", "norm", "o")
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """Matrix memory with an exponential input gate, stabilised by a running maximum m (starting at 0).
+
+    q = W_q h dim^-1/2, k = W_k h (heads x dim), v = W_v h (heads x vdim); per head i = cap tanh((W_i h + b_i) / cap),
+    f = logsigmoid(cap tanh((W_f h + b_f) / cap)); m' = max(f + m, i); S <- e^(f+m-m') S + e^(i-m') k v^T; n likewise
+    with k; o = S^T q / (max(|n.q|, e^-m') + denom_eps); out = W_o (rms_head(o) * norm * sigmoid(W_g h)).
+    `names`: (q, k, v, g, o, norm, i, i bias, f, f bias)."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+    eps: float
+    denom_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o", "norm", "i", "i.b", "f", "f.b")
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule with one decay per head and key channel.
+
+    q = W_q h, k = W_k h (kv_heads x dim), v = W_v h (heads x vdim), each through a causal convolution of `conv` taps
+    (no bias) and silu; q, k -> x / sqrt(sum x^2 + unit_eps), q also times dim^-1/2; beta = sigmoid(W_b h);
+    g = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias)) (heads x dim); S <- diag(g) S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q; out = W_o (rms_head(o) * norm * sigmoid(W_g2 W_g1 h)), norm of vdim entries shared by heads.
+    `rank`: the width of both low-rank pairs.  `names`: (q, k, v, conv suffix, b, A_log, norm, a1, a2, dt_bias, g1, g2, o)."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int
+    gate_rank: int
+    eps: float
+    unit_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", ".conv", "b", "A_log", "norm", "a1", "a2", "dt_bias", "g1", "g2", "o")
+    kind: str = "delta_rule"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side on the same input: left_scale * left(h) + right_scale * right(h).  Each keeps its own
+    cache or state; their tensors lie under `prefixes`."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    prefixes: Tuple[str, str] = ("left.", "right.")
+    kind: str = "parallel_mixer"
+
+
+@dataclass(frozen=True)
+class HyperConnectionSpec:
+    """The learned numbers of one sub-layer of a block with several streams: `in` [streams], `out` [streams],
+    `mix` [streams, streams] (indexed [from, to]), named `<prefix><name>`."""
+    streams: int
+    names: Tuple[str, str, str] = ("in", "out", "mix")
 
 
 @dataclass(frozen=True)
@@ -181,12 +286,19 @@ class SwiGLUSpec:
 class BlockSpec:
     """kind "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)).
     kind "post_norm": x += norm1(mixer(x)); x += norm2(ffn(x)): the sub-layers read the stream itself and
-    their OUTPUTS are normed; `ffn` may be None (the block is then its mixer alone, and norm2 is unused)."""
+    their OUTPUTS are normed; `ffn` may be None (the block is then its mixer alone, and norm2 is unused).
+    kind "hyper_connection": `streams` copies x_1..x_S of the stream (all equal to the single stream when the first
+    such block meets it); sub-layer q reads u = sum_s in_q[s] x_s through its norm and writes
+    x_t <- sum_s mix_q[s, t] x_s + out_q[t] y; the single stream is the sum of the copies.  `hyper`: the two
+    sub-layers' `HyperConnectionSpec`; `hyper_prefixes`: where their tensors lie.  `ffn` may be None."""
     mixer: object
     ffn: object
     norm1: NormSpec
     norm2: NormSpec
     kind: str = "pre_norm"
+    streams: int = 1
+    hyper: Optional[Tuple[object, object]] = None
+    hyper_prefixes: Tuple[str, str] = ("hc1.", "hc2.")
     # tensor-name prefixes of the four parts inside a layer (norm1, mixer, norm2, feed-forward)
     names: Tuple[str, str, str, str] = ("input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp.")
 

@@ -108,6 +108,10 @@ def random_tensors(declared: dict, seed: int, std: float = 0.02, norm_std: float
             t = t.mul_(norm_std).add_(1.0)
         elif decl.init == "linear":
             t = t.mul_(std)
+        elif decl.init in ("conv", "unit"):
+            t = t.mul_(0.5)
+        elif decl.init == "identity":
+            t = t.mul_(norm_std).add_(torch.eye(decl.shape[0], device=t.device))
         else:
             raise ValueError(f"unknown init {decl.init!r} for {name}")
         out[name] = t.to(torch.float32 if decl.store == "float32" else dtype)
