@@ -647,7 +647,7 @@ def test_a_head_norm_that_offers_neither_form_is_refused_when_the_model_is_built
         with pytest.raises(TypeError, match="head norm"):
             cls(spec, w, BuildContext(torch.device(DEV), torch.bfloat16))
         with pytest.raises(ValueError, match="head_dim"):
-            cls(AttentionSpec(32, 2, 1, 24), {}, BuildContext(torch.device(DEV), torch.bfloat16))
+            cls(AttentionSpec(32, 2, 1, 272), {}, BuildContext(torch.device(DEV), torch.bfloat16))     # 24 would be padded to 32
     finally:
         NORMS.unregister("toy_useless")
 
