@@ -73,8 +73,21 @@ CONFIGS = {
                       layer("channel_delta", delta(4, 1, 128, 32, 3, 16, 16), moe(64, 8, 2, 4, 2)),
                       layer("mlstm", mlstm(4, 64, 96, 12.0), dense(136, 1.0))]),
 }
-PAGE = {"A": 8, "B": 16, "C": 64}
-SEED = {"A": 21, "B": 22, "C": 23}
+# D: sizes that are multiples of two at best: key heads of 20 and value heads of 12 numbers (padded to 32 for the kernels),
+#    three rotated pairs, a state of 10 rows, ONE tap (a convolution without memory), every expert chosen, two streams.
+# E: no attention anywhere (the engine then keeps no pages at all), and F: nothing but attention layers.
+CONFIGS["D"] = dict(architecture="Tuzisun", vocab=97, width=72, streams=2, norm=dict(eps=2e-5),
+                    layers=[layer("parallel", parallel(6, 3, 20, 12, 5, 6, 50.0, 0.9, 2, 6, 10, 2, 1, 2, 1.1, 0.3), moe(20, 5, 5)),
+                            layer("mlstm", mlstm(1, 10, 14, 3.0), dense(52, 0.5)),
+                            layer("channel_delta", delta(3, 3, 12, 10, 1, 3, 2), None)])
+CONFIGS["E"] = dict(architecture="Tuzisun", vocab=120, width=48, streams=2, norm=dict(eps=1e-6),
+                    layers=[layer("mlstm", mlstm(2, 16, 16, 10.0), dense(64, 1.0)),
+                            layer("channel_delta", delta(2, 1, 16, 24, 3, 4, 4), moe(16, 4, 2, 2, 1))])
+CONFIGS["F"] = dict(architecture="Tuzisun", vocab=120, width=48, streams=5, norm=dict(eps=1e-6),
+                    layers=[layer("parallel", parallel(2, 2, 16, 16, 1, 16, 10000.0, 0.25, 2, 8, 16, 1, 4, 1, 1.0, 1.0), None),
+                            layer("parallel", parallel(4, 1, 32, 32, 300, 8, 123.0, 0.2, 1, 16, 32, 1, 2, 2, 0.0, 1.0), dense(40, 3.0))])
+PAGE = {"A": 8, "B": 16, "C": 64, "D": 4, "E": 8, "F": 16}
+SEED = {"A": 21, "B": 22, "C": 23, "D": 24, "E": 25, "F": 26}
 TOL = {"float32": 3e-5, "bfloat16": 4e-2}
 # C (sums over 128 and more products, a matrix memory whose denominator cancels): the plain implementation run in
 # float32 already differs from itself in float64 by 4e-5 of the largest logit, three times what A shows
@@ -84,7 +97,7 @@ TOL_OF = {("C", "float32"): 1.5e-4, ("A", "bfloat16"): 6e-2, ("C", "bfloat16"): 
 
 def tol(which, dtype):
     return TOL_OF.get((which, dtype), TOL[dtype])
-CASES = [(w, d) for w in ("A", "B", "C") for d in ("float32", "bfloat16")]
+CASES = [(w, d) for w in ("A", "B", "C", "D", "E", "F") for d in ("float32", "bfloat16")]
 
 
 def edited(cfg, scale=1.0, window=0):
@@ -501,7 +514,7 @@ def test_whole_prompts(which, dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E", "F"])
 def test_stream_after_every_layer(which):
     from vllm_lite_b200.engine import StepEntry
     toks = tokens_for(which, 29, 5)
@@ -577,7 +590,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(which, dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E", "F"])
 def test_cuts_and_batches_agree_bitwise_in_float32(which):
     reqs, schedule = mixed_schedule(which)
     runner = make_runner(which, "float32", num_pages=4 * pages_for(which, 90), max_requests=3)
