@@ -428,7 +428,8 @@ KIKEPEL_SIZES = {"2k": (2048, 16, 128, 128, 768, 128, 1024, 8192, 1024, 32, 4, 6
 TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_decode", "gemm_heads", "gemm_grouped",
              "gemm_grouped_fused", "gemm_grouped_tc5", "gemm_bf16_small_m", "gemm_bf16_tc5", "gemm_bf16_tc5_pair", "layernorm_add",
              "layernorm_rows", "add_rmsnorm", "latent_norm_write", "qk_norm_rope_write", "moe_route", "moe_align",
-             "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias")
+             "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias",
+             "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum")
 
 
 def kikepel_config(size, layers):
@@ -573,6 +574,115 @@ def kikepel_bench(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------
+# --tuzisun: the Tuzisun decoder (several residual streams, tanh norm, window attention beside a state space,
+# matrix memory, channel-wise delta rule, grouped router) beside the Qwen3 decoder at equal width, depth and heads
+# ---------------------------------------------------------------------------------------------------
+# name: (width, streams, attention heads, kv heads, head size, window, state-space heads, their vdim, state, taps,
+#        matrix-memory heads, dim, vdim, delta heads, dim, vdim, low rank, dense ff, expert ff, experts, top, groups, kept, vocab)
+TUZISUN_SIZES = {"2k": (2048, 4, 16, 4, 128, 1024, 32, 64, 128, 4, 8, 128, 256, 16, 128, 128, 64, 8192, 1024, 32, 4, 4, 2, 65536),
+                 "4k": (4096, 4, 32, 8, 128, 4096, 64, 64, 128, 4, 16, 128, 256, 32, 128, 128, 128, 12288, 1408, 64, 6, 8, 4, 65536)}
+
+
+def tuzisun_config(size, layers):
+    (W, S, H, KV, D, win, SH, SP, N, taps, MH, MD, MP, DH, DD, DP, rank, ff, eff, E, top, groups, keep, vocab) = TUZISUN_SIZES[size]
+    par = dict(left=dict(heads=H, kv_heads=KV, dim=D, vdim=D, scale=D ** -0.5, mask=dict(size=win), rot=dict(dims=D, base=250000.0)),
+               right=dict(heads=SH, vdim=SP, state=N, groups=1, conv=taps, norm_groups=8), left_scale=0.8, right_scale=0.9)
+    moe = dict(kind="moe", expert=dict(ff=eff), router=dict(experts=E, top=top, groups=dict(count=groups, keep=keep)))
+    dense = dict(kind="dense", ff=ff, limit=7.0)
+    kinds = [("channel_delta", dict(heads=DH, kv_heads=DH, dim=DD, vdim=DP, conv=taps, decay_rank=rank, gate_rank=rank), dense),
+             ("parallel", par, moe), ("mlstm", dict(heads=MH, dim=MD, vdim=MP, gate_cap=15.0), dense), ("parallel", par, moe)]
+    return dict(architecture="Tuzisun", vocab=vocab, width=W, streams=S, norm=dict(eps=1e-6), max_position_embeddings=16384,
+                layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=kinds[i % 4][2]) for i in range(layers)])
+
+
+def tuzisun_bench(args):
+    import torch
+    from vllm_lite_b200.engine import LLMEngine, StepEntry, random_model
+    size, layers = args.tuzisun, args.layers or 8
+    (W, S, H, KV, D, win, SH, SP, N, taps, MH, MD, MP, DH, DD, DP, rank, ff, eff, E, top, groups, keep, vocab) = TUZISUN_SIZES[size]
+    context, pk = args.context, peaks()
+    warmup = max(args.warmup, 3)
+    qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=KV,
+                head_dim=D, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=16384)
+    results = {}
+    for name, cfg in (("tuzisun", tuzisun_config(size, layers)), ("qwen3", qwen)):
+        _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        slack = 256
+        pages = 64 * (-(-(context + slack) // args.block_size) + 1) + PREFILL_TOKENS // args.block_size + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size,
+                           max_batch_size=64, max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
+                           max_model_len=context + slack)
+        del weights
+        runner, sampler = engine.runner, engine.sampler
+        for t in runner.storage.paged:
+            t.normal_()
+        res = {}
+        pms = prefill_run(runner, vocab)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tokens_per_s": round(PREFILL_TOKENS / pms * 1e3, 1)}
+        for b in (8, 64):
+            ms, launches, _ = decode_run(runner, sampler, b, context, warmup, args.steps, "random", vocab, f"d{b}.")
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b * 1e3 / ms, 1), "launches": round(launches)}
+        gen = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        res["kernels_prefill"] = timed_step(runner, [StepEntry("kp", prompt, [PREFILL_TOKENS - 1])])
+        runner.release("kp")
+        ids = [f"kd{i}" for i in range(64)]
+        for rid in ids:
+            runner.cache.admit(rid)
+            runner.cache.append(rid, context - 1)
+        runner.storage.zero_slots(runner.cache.take_fresh_slots())
+        res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+        for rid in ids:
+            runner.release(rid)
+        runner.check_device_errors()
+        res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
+        results[name] = res
+        del engine, runner, sampler
+        torch.cuda.empty_cache()
+    # ---- the new kernels against their rooflines, beside the like kernels of the closest model ---------
+    T, B = PREFILL_TOKENS, 64
+    t, q = results["tuzisun"], results["qwen3"]
+    def per(res, step, name):
+        n, micro = res[step].get(name, [0, 0.0])
+        return n, micro
+    gb = lambda nbytes, micro: round(nbytes / (micro * 1e-6) / 1e9, 1) if micro else None
+    n_par = sum(1 for i in range(layers) if i % 4 in (1, 3))
+    n_delta = sum(1 for i in range(layers) if i % 4 == 0)
+    n_mm = sum(1 for i in range(layers) if i % 4 == 2)
+    conv_ch = {"ssm": SH * SP + 2 * N, "delta": 2 * DH * DD + DH * DP}
+    roof = {}
+    for step, rows in (("kernels_prefill", T), ("kernels_decode_b64", B)):
+        r = {}
+        n, micro = per(t, step, "hc_step")
+        # a pass reads and writes S float32 copies, reads y and writes h (the first pass of a step reads one copy, the last writes a sum)
+        r["hc_step_gbs"] = gb(n * rows * W * (8.0 * S + 4.0), micro)
+        n, micro = per(q, step, "add_rmsnorm")
+        r["qwen3_add_rmsnorm_gbs"] = gb(n * rows * W * 12.0, micro)
+        n, micro = per(t, step, "short_conv")
+        r["short_conv_gbs"] = gb(rows * 6.0 * (n_par * conv_ch["ssm"] + n_delta * conv_ch["delta"]), micro)
+        n, micro = per(t, step, "gate_norm")
+        r["gate_norm_gbs"] = gb(rows * 8.0 * (n_par * SH * SP + n_delta * DH * DP + n_mm * MH * MP), micro)
+        for op, heads, rows_, cols, count in (("ssd_scan", SH, N, SP, n_par), ("mlstm_scan", MH, MD, MP, n_mm), ("delta_scan", DH, DD, DP, n_delta)):
+            n, micro = per(t, step, op)
+            flops = {"ssd_scan": 4.0, "mlstm_scan": 4.0, "delta_scan": 7.0}[op] * heads * rows_ * cols * rows * count
+            state = 8.0 * heads * rows_ * cols * count * (B if step.endswith("b64") else 1)
+            r[op] = {"us_a_layer": round(micro / max(n, 1), 1), "gflops": round(flops / (micro * 1e-6) / 1e9, 1) if micro else None,
+                     "state_gbs": gb(state, micro)}
+        roof[step] = r
+    roof["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    print(json.dumps({"tuzisun_bench": size, "layers": layers, "context": context, "steps": args.steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, uniform token ids)",
+                      "config": {"tuzisun": dict(zip(("width", "streams", "heads", "kv_heads", "dim", "window", "ssm_heads", "ssm_vdim",
+                                                      "state", "taps", "mm_heads", "mm_dim", "mm_vdim", "delta_heads", "delta_dim",
+                                                      "delta_vdim", "low_rank", "dense_ff", "expert_ff", "experts", "top", "groups",
+                                                      "kept", "vocab"), TUZISUN_SIZES[size])),
+                                 "qwen3": {k_: qwen[k_] for k_ in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                                    "head_dim", "intermediate_size", "vocab_size")}},
+                      "results": results, "roofline": roof}))
+    return 0
+
+
 def _tensors_of(model):
     """Every device tensor that the parts of a model hold (weights as they are resident)."""
     import torch
@@ -615,6 +725,10 @@ def main(argv=None):
                          "default for --size 32b); default otherwise: what the largest batch needs at --context")
     ap.add_argument("--read-ceiling", action="store_true",
                     help="instead of timing steps: every kernel of a decode step alone beside a kernel that only reads as many bytes")
+    ap.add_argument("--tuzisun", default=None, choices=sorted(TUZISUN_SIZES), metavar="SIZE",
+                    help="instead of the default workload: the Tuzisun decoder at layer sizes " + ", ".join(sorted(TUZISUN_SIZES))
+                         + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
+                           "and 64, and every kernel of a step between CUDA events (--layers, default 8; --context, --steps)")
     ap.add_argument("--kikepel", default=None, choices=sorted(KIKEPEL_SIZES), metavar="SIZE",
                     help="instead of the default workload: the Kikepel decoder at layer sizes " + ", ".join(sorted(KIKEPEL_SIZES))
                          + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
@@ -631,6 +745,8 @@ def main(argv=None):
 
     if args.kikepel:
         return kikepel_bench(args)
+    if args.tuzisun:
+        return tuzisun_bench(args)
     import torch
     from vllm_lite_b200.csrc import ops
     from vllm_lite_b200.engine import LLMEngine, random_model

@@ -101,7 +101,7 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("hyper", "vl_dyt_rows"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "vl_short_conv"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
-                                     c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+                                     c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     ("recurrent", "vl_ssd_scan"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("recurrent", "vl_mlstm_scan"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -956,7 +956,7 @@ def sample(logits, temperature, top_k, top_p, uniform, out_token, out_logprob=No
 
 
 # ---------------------------------------------------------------- several residual streams, tanh norm
-HC_MAX_STREAMS = 8
+HC_MAX_STREAMS = 16
 
 
 def hc_step(streams, *, single=None, y=None, mix=None, out_w=None, in_w=None, norm=None, h=None, total=None):
@@ -1034,10 +1034,17 @@ def scan_column_tiles(n: int, columns: int) -> int:
     return -(-columns // ct)
 
 
+def scan_state_floats(H, n, P) -> int:
+    """Floats of a recurrence's state (H heads of n x P numbers) in the layout the scan kernels keep it in: per head
+    and tile of columns, the rows each lane holds, thread by thread."""
+    return H * scan_column_tiles(n, P) * RC_ROWS * RC_THREADS
+
+
 def mlstm_state_floats(H, D, P) -> int:
-    """S [H, D, P], then a normaliser [D] and a running maximum for every tile of columns of every head."""
+    """The matrix memory's state: S as `scan_state_floats`, then a normaliser [D] and a running maximum for every tile
+    of columns of every head."""
     Z = scan_column_tiles(D, P)
-    return H * D * P + H * Z * D + H * Z
+    return scan_state_floats(H, D, P) + H * Z * D + H * Z
 
 
 def _state_args(state, state_off, need):
@@ -1055,9 +1062,10 @@ def _seg_args(cu, slots):
     return B
 
 
-def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=True):
+def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=True, longest=None):
     """out float32 [T, C] = act(causal convolution over time of columns col0 .. col0+C of x [T, ld]); weight float32
-    [C, taps]; the last taps-1 inputs live at `state_off` of every request's state row [(taps-1), C]."""
+    [C, taps]; the last taps-1 inputs live at `state_off` of every request's state row [(taps-1), C].  `longest`: a
+    bound on the tokens one request brings (default: all of them)."""
     _need(x, None, "x", 2); _need(weight, torch.float32, "weight", 2); _need(out, torch.float32, "out", 2)
     taps = weight.shape[1]
     if weight.shape[0] != C or out.shape != (x.shape[0], C):
@@ -1067,8 +1075,8 @@ def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=T
     B = _seg_args(cu, slots)
     sp, stride = _state_args(state, state_off, (taps - 1) * C)
     _check(_fn("recurrent", "vl_short_conv")(_ptr(x), dtype_code(x.dtype), x.shape[1], col0, C, _ptr(weight), _ptr(bias), taps,
-                                             sp, stride, _ptr(cu), _ptr(slots), B, _ptr(out), int(bool(act)), _stream()),
-           "vl_short_conv")
+                                             sp, stride, _ptr(cu), _ptr(slots), B, int(longest or max(x.shape[0], 1)), _ptr(out),
+                                             int(bool(act)), _stream()), "vl_short_conv")
     return out
 
 
@@ -1082,8 +1090,7 @@ def ssd_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, state_off, cu, slots, 
     if proj.shape[0] != T or y.shape != (T, H * P) or dt_col + H > proj.shape[1]:
         raise KernelError("ssd_scan: shapes disagree")
     B = _seg_args(cu, slots)
-    sp, stride = _state_args(state, state_off, H * N * P)
-    scan_lanes(N)
+    sp, stride = _state_args(state, state_off, scan_state_floats(H, N, P))
     _check(_fn("recurrent", "vl_ssd_scan")(_ptr(xbc), xbc.shape[1], _ptr(proj), dtype_code(proj.dtype), proj.shape[1], dt_col,
                                            _ptr(dt_bias), _ptr(A_log), _ptr(D), sp, stride, _ptr(cu), _ptr(slots), B, _ptr(y),
                                            H, G, N, P, _stream()), "vl_ssd_scan")
@@ -1114,8 +1121,7 @@ def delta_scan(qkv, decay, decay_col, dt_bias, A_log, proj, beta_col, q_scale, u
             or A_log.shape[0] != H or beta_col + H > proj.shape[1]:
         raise KernelError("delta_scan: shapes disagree")
     B = _seg_args(cu, slots)
-    sp, stride = _state_args(state, state_off, H * D * P)
-    scan_lanes(D)
+    sp, stride = _state_args(state, state_off, scan_state_floats(H, D, P))
     _check(_fn("recurrent", "vl_delta_scan")(_ptr(qkv), qkv.shape[1], _ptr(decay), decay.shape[1], decay_col, _ptr(dt_bias), _ptr(A_log), _ptr(proj),
                                              dtype_code(proj.dtype), proj.shape[1], beta_col, float(q_scale), float(unit_eps),
                                              sp, stride, _ptr(cu), _ptr(slots), B, _ptr(o), H, G, D, P, _stream()),

@@ -7,7 +7,8 @@
 // decays and their logarithms, softplus and exponentials, step sizes, gates, unit norms and the state.
 //
 //   vl_short_conv   out[t, c] = act(bias[c] + sum_j w[c, j] in[t - (taps-1) + j, c]), zeros before a request's
-//                   first token; the last taps-1 inputs of every channel are part of the state
+//                   first token; the last taps-1 inputs of every channel are part of the state (`longest`: a bound
+//                   on the tokens a request brings, which says how many blocks share a request)
 //   vl_ssd_scan     S <- exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x          (S: N x P per head, dt =
 //                   softplus(raw + bias); heads share B and C in groups)
 //   vl_mlstm_scan   m' = max(f + m, i);  S <- e^(f+m-m') S + e^(i-m') k v^T;  n likewise with k alone;
@@ -20,12 +21,12 @@
 // Layout of the scans: a block owns (head, request, tile of value columns); a column of the state is held in
 // registers by L lanes of a warp (row r of the state by lane r mod L), so a token costs each lane N/L
 // multiply-adds and one or two butterfly sums over the L lanes.  The per-token vectors of a chunk of tokens
-// are staged in shared memory by the whole block.  The order of every sum depends on the sizes alone.
+// are staged in shared memory by the whole block, one chunk ahead of the walk.  The order of every sum depends
+// on the sizes alone, never on how the tokens were cut into steps or on what else the launch holds.
 #include "common.cuh"
 
 #define RC_THREADS 128
 #define RC_ROWS 16            // state rows per lane, at most
-#define RC_CHUNK 8            // tokens staged at a time
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
@@ -41,22 +42,29 @@ static inline int lanes_for(int N) {
 }
 
 // ------------------------------------------------------------------------------------------ convolution
+// A block owns 32 channels and CONV_TOKENS tokens of one request.  mode 0: outputs and the new state by the same block
+// (every request brings at most CONV_TOKENS tokens: one block per request and channel tile, so nobody else reads
+// the state it rewrites); mode 1: outputs only; mode 2: the new state only (a launch of its own after mode 1, when
+// requests are cut among several blocks: the blocks that read the old state must have finished).
+#define CONV_TOKENS 64
 template <typename TP>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const float* __restrict__ w,
                   const float* __restrict__ bias, int taps, float* __restrict__ state, long long state_stride,
-                  const int* __restrict__ cu, const int* __restrict__ slots, float* __restrict__ out, int act) {
+                  const int* __restrict__ cu, const int* __restrict__ slots, float* __restrict__ out, int act, int mode) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
     const int s0 = cu[b], n = cu[b + 1] - s0;
-    if (n <= 0) return;
+    const int first = blockIdx.z * CONV_TOKENS;
+    if (n <= 0 || first >= n) return;
+    const int last = mode == 0 ? n : min(n, first + CONV_TOKENS);
     const int c = blockIdx.x * 32 + threadIdx.x;
     const bool live = c < C;
     float* st = state + (long long)slots[b] * state_stride;          // [(taps-1), C]
     const int back = taps - 1;
-    if (live) {
-        for (int t = threadIdx.y; t < n; t += blockDim.y) {
+    if (live && mode != 2) {
+        for (int t = first + threadIdx.y; t < last; t += blockDim.y) {
             float acc = bias ? bias[c] : 0.f;
             for (int j = 0; j < taps; ++j) {
                 const int at = t - back + j;
@@ -66,6 +74,7 @@ short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const floa
             out[(size_t)(s0 + t) * C + c] = act ? silu_f(acc) : acc;
         }
     }
+    if (mode == 1) return;
     __syncthreads();
     if (live && threadIdx.y == 0) {
         for (int j = 0; j < back; ++j) {                              // reads run ahead of the writes
@@ -77,29 +86,77 @@ short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const floa
 
 extern "C" int vl_short_conv(const void* in, int dtype, int ld, int col0, int C, const float* w, const float* bias,
                              int taps, float* state, long long state_stride, const int* cu, const int* slots,
-                             int B, float* out, int act, void* stream) {
+                             int B, int longest, float* out, int act, void* stream) {
     if (B <= 0 || C <= 0) return VL_OK;
-    if (taps <= 0 || col0 < 0 || col0 + C > ld) return VL_ERR_ARGUMENT;
-    dim3 grid((C + 31) / 32, B), block(32, 8);
+    if (taps <= 0 || col0 < 0 || col0 + C > ld || longest <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return vl_launch(short_conv_kernel<float>, grid, block, 0, s, (const float*)in, ld, col0, C, w, bias, taps, state,
-                         state_stride, cu, slots, out, act);
-    if (dtype == VL_BF16)
-        return vl_launch(short_conv_kernel<bf16>, grid, block, 0, s, (const bf16*)in, ld, col0, C, w, bias, taps, state,
-                         state_stride, cu, slots, out, act);
-    return VL_ERR_UNSUPPORTED;
+    const int cuts = (longest + CONV_TOKENS - 1) / CONV_TOKENS;
+    for (int pass = 0; pass < (cuts > 1 ? 2 : 1); ++pass) {
+        const int mode = cuts > 1 ? pass + 1 : 0;
+        dim3 grid((C + 31) / 32, B, mode == 1 ? cuts : 1), block(32, 8);
+        int rc;
+        if (dtype == VL_F32)
+            rc = vl_launch(short_conv_kernel<float>, grid, block, 0, s, (const float*)in, ld, col0, C, w, bias, taps, state,
+                           state_stride, cu, slots, out, act, mode);
+        else if (dtype == VL_BF16)
+            rc = vl_launch(short_conv_kernel<bf16>, grid, block, 0, s, (const bf16*)in, ld, col0, C, w, bias, taps, state,
+                           state_stride, cu, slots, out, act, mode);
+        else
+            return VL_ERR_UNSUPPORTED;
+        if (rc) return rc;
+    }
+    return VL_OK;
+}
+
+// ------------------------------------------------------------------------------------------ the scans' frame
+// A scan block stages the per-token vectors of a chunk of tokens in shared memory, [chunk][VEC] floats.  The values of
+// the NEXT chunk are loaded into registers before the tokens of this chunk are walked and stored to the other buffer
+// afterwards, so the loads' latency hides behind the walk (RC_PREFETCH values per thread, which bounds the chunk).
+// A request's state lies in the order the block's threads hold it: [head][column tile][row i of a lane][thread], so
+// that loading and storing it are contiguous; the layout is the kernels' own business (vl_scan_state_floats).
+#define RC_PREFETCH 24
+
+template <typename Raw>
+__device__ __forceinline__ void scan_prefetch(float (&pf)[RC_PREFETCH], int first_row, int m, int VEC, Raw raw) {
+#pragma unroll
+    for (int j = 0; j < RC_PREFETCH; ++j) {
+        const int idx = threadIdx.x + j * RC_THREADS;
+        if (idx < m * VEC) {
+            const int k = idx / VEC;
+            pf[j] = raw(first_row + k, idx - k * VEC);
+        }
+    }
+}
+__device__ __forceinline__ void scan_commit(const float (&pf)[RC_PREFETCH], float* buf, int m, int VEC) {
+#pragma unroll
+    for (int j = 0; j < RC_PREFETCH; ++j) {
+        const int idx = threadIdx.x + j * RC_THREADS;
+        if (idx < m * VEC) buf[idx] = pf[j];
+    }
+}
+static inline int scan_chunk(int VEC) {
+    int m = RC_PREFETCH * RC_THREADS / VEC;
+    return m < 1 ? 0 : (m > 16 ? 16 : m);
+}
+__device__ __forceinline__ float* scan_state(float* state, long long stride, int slot, int h) {
+    return state + (long long)slot * stride + ((size_t)h * gridDim.z + blockIdx.z) * RC_ROWS * RC_THREADS + threadIdx.x;
+}
+extern "C" long long vl_scan_state_floats(int H, int N, int P) {
+    const int L = lanes_for(N);
+    if (L > 32 || H <= 0 || N <= 0 || P <= 0) return -1;
+    const int CT = RC_THREADS / L, Z = (P + CT - 1) / CT;
+    return (long long)H * Z * RC_ROWS * RC_THREADS;
 }
 
 // ------------------------------------------------------------------------------------------ state space
-// xbc float32 [T, C]: x (H*P) | B (G*N) | C (G*N), the convolution's output.  raw_dt: column dt_col + h of `proj`.
-// state [slots][H][N][P].  y float32 [T, H*P].
+// xbc float32 [T, C]: x (H*P) | B (G*N) | C (G*N), the convolution's output.  raw dt: column dt_col + h of `proj`.
+// y float32 [T, H*P].  Staged per token: B [N] | C [N] | x [CT] | dt | decay.
 template <typename TP>
 __global__ void __launch_bounds__(RC_THREADS)
 ssd_scan_kernel(const float* __restrict__ xbc, int C, const TP* __restrict__ proj, int ld, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dw,
                 float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                const int* __restrict__ slots, float* __restrict__ y, int H, int G, int N, int P, int L) {
+                const int* __restrict__ slots, float* __restrict__ y, int H, int G, int N, int P, int L, int chunk) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -111,58 +168,65 @@ ssd_scan_kernel(const float* __restrict__ xbc, int C, const TP* __restrict__ pro
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
     const int g = h / (H / G), inner = H * P;
-    float* sB = sm;                               // [chunk][N]
-    float* sC = sB + RC_CHUNK * N;                // [chunk][N]
-    float* sX = sC + RC_CHUNK * N;                // [chunk][CT]
-    float* sDt = sX + RC_CHUNK * CT;              // [chunk]
-    float* sA = sDt + RC_CHUNK;                   // [chunk]
-    float* S = state + (long long)slots[b] * state_stride + (size_t)h * N * P;
+    const int VEC = 2 * N + CT + 2;
+    float* S = scan_state(state, state_stride, slots[b], h);
     float s[RC_ROWS];
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
-        const int r = l + L * i;
-        s[i] = (live && r < N) ? S[(size_t)r * P + p] : 0.f;
-    }
+    for (int i = 0; i < RC_ROWS; ++i) s[i] = S[(size_t)i * RC_THREADS];
     const float rate = expf(A_log[h]), skip = Dw[h], bias = dt_bias[h];
-    for (int t0 = 0; t0 < n; t0 += RC_CHUNK) {
-        const int m = min(RC_CHUNK, n - t0);
-        __syncthreads();
-        for (int i = tid; i < m * N; i += RC_THREADS) {
-            const int k = i / N, r = i - k * N;
-            const float* row = xbc + (size_t)(s0 + t0 + k) * C + inner + (size_t)g * N + r;
-            sB[k * N + r] = row[0];
-            sC[k * N + r] = row[(size_t)G * N];
-        }
-        for (int i = tid; i < m * CT; i += RC_THREADS) {
-            const int k = i / CT, c = i - k * CT;
-            sX[i] = p0 + c < P ? xbc[(size_t)(s0 + t0 + k) * C + (size_t)h * P + p0 + c] : 0.f;
-        }
+    auto raw = [&](int row, int e) -> float {
+        const float* src = xbc + (size_t)(s0 + row) * C;
+        if (e < 2 * N) return src[inner + (e < N ? (size_t)g * N + e : (size_t)(G + g) * N + (e - N))];
+        if (e < 2 * N + CT) return p0 + (e - 2 * N) < P ? src[(size_t)h * P + p0 + (e - 2 * N)] : 0.f;
+        return e == 2 * N + CT ? to_f32(proj[(size_t)(s0 + row) * ld + dt_col + h]) : 0.f;
+    };
+    auto finish = [&](float* buf, int m) {                            // dt = softplus(raw + bias), decay = exp(-rate dt)
         if (tid < m) {
-            const float dt = softplus_f(to_f32(proj[(size_t)(s0 + t0 + tid) * ld + dt_col + h]) + bias);
-            sDt[tid] = dt;
-            sA[tid] = expf(-rate * dt);
+            float* v = buf + (size_t)tid * VEC + 2 * N + CT;
+            const float dt = softplus_f(v[0] + bias);
+            v[0] = dt;
+            v[1] = expf(-rate * dt);
         }
-        __syncthreads();
+    };
+    float pf[RC_PREFETCH];
+    int m = min(chunk, n);
+    scan_prefetch(pf, 0, m, VEC, raw);
+    scan_commit(pf, sm, m, VEC);
+    __syncthreads();
+    finish(sm, m);
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk) {
+        const int mn = min(chunk, n - t0 - m);                        // tokens of the next chunk
+        if (mn > 0) scan_prefetch(pf, t0 + m, mn, VEC, raw);
+        const float* buf = sm + (size_t)cur * chunk * VEC;
         for (int k = 0; k < m; ++k) {
-            const float a = sA[k], xv = sX[k * CT + col], dx = sDt[k] * xv;
+            const float* v = buf + (size_t)k * VEC;
+            const float xv = v[2 * N + col], dx = v[2 * N + CT] * xv, a = v[2 * N + CT + 1];
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < RC_ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < N) {
-                    s[i] = a * s[i] + sB[k * N + r] * dx;
-                    acc += s[i] * sC[k * N + r];
+                    s[i] = a * s[i] + v[r] * dx;
+                    acc += s[i] * v[N + r];
                 }
             }
             acc = group_sum(acc, L);
             if (live && l == 0) y[(size_t)(s0 + t0 + k) * inner + (size_t)h * P + p] = acc + skip * xv;
         }
+        if (mn > 0) {
+            float* nxt = sm + (size_t)(cur ^ 1) * chunk * VEC;
+            scan_commit(pf, nxt, mn, VEC);
+            __syncthreads();
+            finish(nxt, mn);
+        }
+        __syncthreads();
+        cur ^= 1;
+        m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
-        const int r = l + L * i;
-        if (live && r < N) S[(size_t)r * P + p] = s[i];
-    }
+    for (int i = 0; i < RC_ROWS; ++i) S[(size_t)i * RC_THREADS] = s[i];
 }
 
 extern "C" int vl_ssd_scan(const float* xbc, int C, const void* proj, int dtype, int ld, int dt_col, const float* dt_bias,
@@ -172,30 +236,33 @@ extern "C" int vl_ssd_scan(const float* xbc, int C, const void* proj, int dtype,
     if (H <= 0 || G <= 0 || H % G || N <= 0 || P <= 0 || C != H * P + 2 * G * N) return VL_ERR_ARGUMENT;
     const int L = lanes_for(N);
     if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L;
+    const int CT = RC_THREADS / L, VEC = 2 * N + CT + 2, chunk = scan_chunk(VEC);
+    if (!chunk) return VL_ERR_UNSUPPORTED;
     dim3 grid(H, B, (P + CT - 1) / CT);
-    const size_t smem = sizeof(float) * (size_t)(RC_CHUNK * (2 * N + CT + 2));
+    const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(ssd_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, xbc, C, (const float*)proj, ld, dt_col,
-                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L);
+                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L, chunk);
     if (dtype == VL_BF16)
         return vl_launch(ssd_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, xbc, C, (const bf16*)proj, ld, dt_col,
-                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L);
+                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------------------------------ matrix memory
 // proj [T, ld]: q at q_col (H*D), k at k_col (H*D), v at v_col (H*P), raw gates at i_col, f_col (H each).
-// state per slot: S [H][D][P], then n [H][Z][D], then m [H][Z], Z = the number of column tiles of a head
+// state per slot: S in the scans' layout, then n [H][Z][D], then m [H][Z], Z = the number of column tiles of a head
 // (vl_mlstm_state_floats): blocks of one head run at different times, so each keeps its own n and m.  o float32 [T, H*P].
+// Staged per token: q [D] (scaled) | k [D] | v [CT] | keep | put | floor  (the raw gates arrive in the first two of these).
 template <typename TP>
 __global__ void __launch_bounds__(RC_THREADS)
 mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale, float den_eps,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int L) {
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int L, int chunk) {
     extern __shared__ float sm[];
+    __shared__ float sM;
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
@@ -205,63 +272,67 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
     const int col = tid / L, l = tid % L;
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
-    float* sQ = sm;                               // [chunk][D]
-    float* sK = sQ + RC_CHUNK * D;                // [chunk][D]
-    float* sV = sK + RC_CHUNK * D;                // [chunk][CT]
-    float* sKeep = sV + RC_CHUNK * CT;            // [chunk]
-    float* sPut = sKeep + RC_CHUNK;               // [chunk]
-    float* sFloor = sPut + RC_CHUNK;              // [chunk]
-    float* sM = sFloor + RC_CHUNK;                // [1]
-    float* base = state + (long long)slots[b] * state_stride;
-    float* S = base + (size_t)h * D * P;
-    const int Z = gridDim.z, z = blockIdx.z;          // every tile of columns keeps n and m for itself
-    float* nv = base + (size_t)H * D * P + ((size_t)h * Z + z) * D;
-    float* mv = base + (size_t)H * D * P + (size_t)H * Z * D + (size_t)h * Z + z;
+    const int VEC = 2 * D + CT + 3;
+    const int Z = gridDim.z, z = blockIdx.z;
+    float* S = scan_state(state, state_stride, slots[b], h);
+    float* base = state + (long long)slots[b] * state_stride + (size_t)H * Z * RC_ROWS * RC_THREADS;
+    float* nv = base + ((size_t)h * Z + z) * D;
+    float* mv = base + (size_t)H * Z * D + (size_t)h * Z + z;
     float s[RC_ROWS], nr[RC_ROWS];
 #pragma unroll
     for (int i = 0; i < RC_ROWS; ++i) {
         const int r = l + L * i;
-        s[i] = (live && r < D) ? S[(size_t)r * P + p] : 0.f;
+        s[i] = S[(size_t)i * RC_THREADS];
         nr[i] = r < D ? nv[r] : 0.f;
     }
-    if (tid == 0) sM[0] = mv[0];
-    for (int t0 = 0; t0 < n; t0 += RC_CHUNK) {
-        const int m = min(RC_CHUNK, n - t0);
-        __syncthreads();
-        for (int i = tid; i < m * D; i += RC_THREADS) {
-            const int k = i / D, r = i - k * D;
-            const TP* row = proj + (size_t)(s0 + t0 + k) * ld + (size_t)h * D + r;
-            sQ[i] = to_f32(row[q_col]) * q_scale;
-            sK[i] = to_f32(row[k_col]);
-        }
-        for (int i = tid; i < m * CT; i += RC_THREADS) {
-            const int k = i / CT, c = i - k * CT;
-            sV[i] = p0 + c < P ? to_f32(proj[(size_t)(s0 + t0 + k) * ld + v_col + (size_t)h * P + p0 + c]) : 0.f;
-        }
+    if (tid == 0) sM = mv[0];
+    const float ib = i_bias[h], fb = f_bias[h];
+    auto raw = [&](int row, int e) -> float {
+        const TP* src = proj + (size_t)(s0 + row) * ld;
+        if (e < D) return to_f32(src[q_col + (size_t)h * D + e]) * q_scale;
+        if (e < 2 * D) return to_f32(src[k_col + (size_t)h * D + (e - D)]);
+        if (e < 2 * D + CT) return p0 + (e - 2 * D) < P ? to_f32(src[v_col + (size_t)h * P + p0 + (e - 2 * D)]) : 0.f;
+        if (e == 2 * D + CT) return to_f32(src[i_col + h]);
+        return e == 2 * D + CT + 1 ? to_f32(src[f_col + h]) : 0.f;
+    };
+    auto finish = [&](float* buf, int m) {                            // the gates and the running maximum, token after token
         if (tid == 0) {
-            float mx = sM[0];
+            float mx = sM;
             for (int k = 0; k < m; ++k) {
-                const TP* row = proj + (size_t)(s0 + t0 + k) * ld + h;
-                const float ig = cap * tanhf((to_f32(row[i_col]) + i_bias[h]) / cap);
-                const float fa = cap * tanhf((to_f32(row[f_col]) + f_bias[h]) / cap);
+                float* v = buf + (size_t)k * VEC + 2 * D + CT;
+                const float ig = cap * tanhf((v[0] + ib) / cap);
+                const float fa = cap * tanhf((v[1] + fb) / cap);
                 const float fg = fminf(fa, 0.f) - log1pf(expf(-fabsf(fa)));          // log sigmoid
                 const float nm = fmaxf(fg + mx, ig);
-                sKeep[k] = expf(fg + mx - nm);
-                sPut[k] = expf(ig - nm);
-                sFloor[k] = expf(-nm);
+                v[0] = expf(fg + mx - nm);
+                v[1] = expf(ig - nm);
+                v[2] = expf(-nm);
                 mx = nm;
             }
-            sM[0] = mx;
+            sM = mx;
         }
-        __syncthreads();
+    };
+    float pf[RC_PREFETCH];
+    int m = min(chunk, n);
+    scan_prefetch(pf, 0, m, VEC, raw);
+    scan_commit(pf, sm, m, VEC);
+    __syncthreads();
+    finish(sm, m);
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk) {
+        const int mn = min(chunk, n - t0 - m);
+        if (mn > 0) scan_prefetch(pf, t0 + m, mn, VEC, raw);
+        const float* buf = sm + (size_t)cur * chunk * VEC;
         for (int k = 0; k < m; ++k) {
-            const float keep = sKeep[k], pv = sPut[k] * sV[k * CT + col], put = sPut[k];
+            const float* v = buf + (size_t)k * VEC;
+            const float keep = v[2 * D + CT], put = v[2 * D + CT + 1], pv = put * v[2 * D + col];
             float acc = 0.f, den = 0.f;
 #pragma unroll
             for (int i = 0; i < RC_ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
-                    const float kv = sK[k * D + r], qv = sQ[k * D + r];
+                    const float kv = v[D + r], qv = v[r];
                     s[i] = keep * s[i] + kv * pv;
                     nr[i] = keep * nr[i] + put * kv;
                     acc += s[i] * qv;
@@ -271,24 +342,32 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
             acc = group_sum(acc, L);
             den = group_sum(den, L);
             if (live && l == 0)
-                o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc / (fmaxf(fabsf(den), sFloor[k]) + den_eps);
+                o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc / (fmaxf(fabsf(den), v[2 * D + CT + 2]) + den_eps);
         }
+        if (mn > 0) {
+            float* nxt = sm + (size_t)(cur ^ 1) * chunk * VEC;
+            scan_commit(pf, nxt, mn, VEC);
+            __syncthreads();
+            finish(nxt, mn);
+        }
+        __syncthreads();
+        cur ^= 1;
+        m = mn;
     }
-    __syncthreads();
 #pragma unroll
     for (int i = 0; i < RC_ROWS; ++i) {
         const int r = l + L * i;
-        if (live && r < D) S[(size_t)r * P + p] = s[i];
+        S[(size_t)i * RC_THREADS] = s[i];
         if (col == 0 && r < D) nv[r] = nr[i];
     }
-    if (tid == 0) mv[0] = sM[0];
+    if (tid == 0) mv[0] = sM;
 }
 
 extern "C" long long vl_mlstm_state_floats(int H, int D, int P) {
     const int L = lanes_for(D);
     if (L > 32 || H <= 0 || D <= 0 || P <= 0) return -1;
     const int CT = RC_THREADS / L, Z = (P + CT - 1) / CT;
-    return (long long)H * D * P + (long long)H * Z * D + (long long)H * Z;
+    return (long long)H * Z * RC_ROWS * RC_THREADS + (long long)H * Z * D + (long long)H * Z;
 }
 
 extern "C" int vl_mlstm_scan(const void* proj, int dtype, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
@@ -299,29 +378,32 @@ extern "C" int vl_mlstm_scan(const void* proj, int dtype, int ld, int q_col, int
     if (H <= 0 || D <= 0 || P <= 0 || !(cap > 0.f)) return VL_ERR_ARGUMENT;
     const int L = lanes_for(D);
     if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L;
+    const int CT = RC_THREADS / L, VEC = 2 * D + CT + 3, chunk = scan_chunk(VEC);
+    if (!chunk) return VL_ERR_UNSUPPORTED;
     dim3 grid(H, B, (P + CT - 1) / CT);
-    const size_t smem = sizeof(float) * (size_t)(RC_CHUNK * (2 * D + CT + 3) + 1);
+    const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(mlstm_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, (const float*)proj, ld, q_col, k_col, v_col,
-                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L);
+                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L, chunk);
     if (dtype == VL_BF16)
         return vl_launch(mlstm_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, (const bf16*)proj, ld, q_col, k_col, v_col,
-                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L);
+                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------------------------------ delta rule
 // qkv float32 [T, C]: q (G*D) | k (G*D) | v (H*P), the convolutions' output.  raw decay: columns dcol .. of `decay` (rows dld wide),
-// raw beta: column beta_col + h of `proj`.  state [slots][H][D][P].  o float32 [T, H*P].
+// raw beta: column beta_col + h of `proj`.  o float32 [T, H*P].
+// Staged per token: q [D] | k [D] | decay [D] | v [CT] | beta; a warp per token then makes q and k unit vectors (q scaled),
+// the decays exp(-rate softplus(raw + bias)) and beta a sigmoid.
 template <typename TP>
 __global__ void __launch_bounds__(RC_THREADS)
 delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ decay, int dld, int dcol,
                   const float* __restrict__ dt_bias,
                   const float* __restrict__ A_log, const TP* __restrict__ proj, int ld, int beta_col, float q_scale,
                   float unit_eps, float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int G, int D, int P, int L) {
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int G, int D, int P, int L, int chunk) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -333,74 +415,84 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ d
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
     const int g = h / (H / G);
-    float* sQ = sm;                               // [chunk][D]
-    float* sK = sQ + RC_CHUNK * D;                // [chunk][D]
-    float* sG = sK + RC_CHUNK * D;                // [chunk][D]
-    float* sV = sG + RC_CHUNK * D;                // [chunk][CT]
-    float* sBeta = sV + RC_CHUNK * CT;            // [chunk]
-    float* S = state + (long long)slots[b] * state_stride + (size_t)h * D * P;
+    const int VEC = 3 * D + CT + 1;
+    float* S = scan_state(state, state_stride, slots[b], h);
     float s[RC_ROWS];
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
-        const int r = l + L * i;
-        s[i] = (live && r < D) ? S[(size_t)r * P + p] : 0.f;
-    }
+    for (int i = 0; i < RC_ROWS; ++i) s[i] = S[(size_t)i * RC_THREADS];
     const float rate = expf(A_log[h]);
-    for (int t0 = 0; t0 < n; t0 += RC_CHUNK) {
-        const int m = min(RC_CHUNK, n - t0);
-        __syncthreads();
-        for (int k = warp; k < m; k += RC_THREADS / 32) {             // a warp per token: unit vectors and decays
-            const size_t t = (size_t)(s0 + t0 + k);
-            const float* qrow = qkv + t * C + (size_t)g * D;
-            const float* krow = qrow + (size_t)G * D;
+    auto raw = [&](int row, int e) -> float {
+        const size_t t = (size_t)(s0 + row);
+        if (e < 2 * D) return qkv[t * C + (e < D ? (size_t)g * D + e : (size_t)(G + g) * D + (e - D))];
+        if (e < 3 * D) return to_f32(decay[t * dld + dcol + (size_t)h * D + (e - 2 * D)]);
+        if (e < 3 * D + CT) return p0 + (e - 3 * D) < P ? qkv[t * C + (size_t)2 * G * D + (size_t)h * P + p0 + (e - 3 * D)] : 0.f;
+        return to_f32(proj[t * ld + beta_col + h]);
+    };
+    auto finish = [&](float* buf, int m) {
+        for (int k = warp; k < m; k += RC_THREADS / 32) {
+            float* v = buf + (size_t)k * VEC;
             float qq = 0.f, kk = 0.f;
-            for (int r = lane; r < D; r += 32) { qq += qrow[r] * qrow[r]; kk += krow[r] * krow[r]; }
+            for (int r = lane; r < D; r += 32) { qq += v[r] * v[r]; kk += v[D + r] * v[D + r]; }
             qq = warp_sum(qq);
             kk = warp_sum(kk);
             const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.f / sqrtf(kk + unit_eps);
             for (int r = lane; r < D; r += 32) {
-                sQ[k * D + r] = qrow[r] * qn;
-                sK[k * D + r] = krow[r] * kn;
-                const float step = softplus_f(to_f32(decay[t * (size_t)dld + dcol + (size_t)h * D + r]) + dt_bias[(size_t)h * D + r]);
-                sG[k * D + r] = expf(-rate * step);
+                v[r] *= qn;
+                v[D + r] *= kn;
+                v[2 * D + r] = expf(-rate * softplus_f(v[2 * D + r] + dt_bias[(size_t)h * D + r]));
             }
-            if (lane == 0) sBeta[k] = sigmoid_f(to_f32(proj[t * ld + beta_col + h]));
+            if (lane == 0) v[3 * D + CT] = sigmoid_f(v[3 * D + CT]);
         }
-        for (int i = tid; i < m * CT; i += RC_THREADS) {
-            const int k = i / CT, c = i - k * CT;
-            sV[i] = p0 + c < P ? qkv[(size_t)(s0 + t0 + k) * C + (size_t)2 * G * D + (size_t)h * P + p0 + c] : 0.f;
-        }
-        __syncthreads();
+    };
+    float pf[RC_PREFETCH];
+    int m = min(chunk, n);
+    scan_prefetch(pf, 0, m, VEC, raw);
+    scan_commit(pf, sm, m, VEC);
+    __syncthreads();
+    finish(sm, m);
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk) {
+        const int mn = min(chunk, n - t0 - m);
+        if (mn > 0) scan_prefetch(pf, t0 + m, mn, VEC, raw);
+        const float* buf = sm + (size_t)cur * chunk * VEC;
         for (int k = 0; k < m; ++k) {
+            const float* v = buf + (size_t)k * VEC;
             float back = 0.f;
 #pragma unroll
             for (int i = 0; i < RC_ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
-                    s[i] *= sG[k * D + r];
-                    back += s[i] * sK[k * D + r];
+                    s[i] *= v[2 * D + r];
+                    back += s[i] * v[D + r];
                 }
             }
             back = group_sum(back, L);
-            const float u = sBeta[k] * (sV[k * CT + col] - back);
+            const float u = v[3 * D + CT] * (v[3 * D + col] - back);
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < RC_ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
-                    s[i] += sK[k * D + r] * u;
-                    acc += s[i] * sQ[k * D + r];
+                    s[i] += v[D + r] * u;
+                    acc += s[i] * v[r];
                 }
             }
             acc = group_sum(acc, L);
             if (live && l == 0) o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc;
         }
+        if (mn > 0) {
+            float* nxt = sm + (size_t)(cur ^ 1) * chunk * VEC;
+            scan_commit(pf, nxt, mn, VEC);
+            __syncthreads();
+            finish(nxt, mn);
+        }
+        __syncthreads();
+        cur ^= 1;
+        m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
-        const int r = l + L * i;
-        if (live && r < D) S[(size_t)r * P + p] = s[i];
-    }
+    for (int i = 0; i < RC_ROWS; ++i) S[(size_t)i * RC_THREADS] = s[i];
 }
 
 extern "C" int vl_delta_scan(const float* qkv, int C, const void* decay, int dld, int dcol, const float* dt_bias, const float* A_log,
@@ -411,16 +503,17 @@ extern "C" int vl_delta_scan(const float* qkv, int C, const void* decay, int dld
     if (H <= 0 || G <= 0 || H % G || D <= 0 || P <= 0 || C != 2 * G * D + H * P) return VL_ERR_ARGUMENT;
     const int L = lanes_for(D);
     if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L;
+    const int CT = RC_THREADS / L, VEC = 3 * D + CT + 1, chunk = scan_chunk(VEC);
+    if (!chunk) return VL_ERR_UNSUPPORTED;
     dim3 grid(H, B, (P + CT - 1) / CT);
-    const size_t smem = sizeof(float) * (size_t)(RC_CHUNK * (3 * D + CT + 1));
+    const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(delta_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, qkv, C, (const float*)decay, dld, dcol, dt_bias, A_log,
-                         (const float*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L);
+                         (const float*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L, chunk);
     if (dtype == VL_BF16)
         return vl_launch(delta_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, qkv, C, (const bf16*)decay, dld, dcol, dt_bias, A_log,
-                         (const bf16*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L);
+                         (const bf16*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -43,7 +43,8 @@ class StateSpace:
     @staticmethod
     def cache_need(s: StateSpaceSpec):
         inner, conv_ch, _ = StateSpace._sizes(s)
-        return FixedState(((s.conv - 1) * conv_ch + s.num_heads * s.state * s.vdim,))
+        from ..csrc import ops
+        return FixedState(((s.conv - 1) * conv_ch + ops.scan_state_floats(s.num_heads, s.state, s.vdim),))
 
     def __init__(self, s: StateSpaceSpec, weights: dict, ctx):
         from ..csrc import ops
@@ -65,7 +66,8 @@ class StateSpace:
         T = h.shape[0]
         proj = self.in_proj(h, step, "ssm.in")
         xbc = ws.get(tag + "ssm.xbc", (T, conv_ch), torch.float32)
-        ops.short_conv(proj, inner, conv_ch, self.conv, self.conv_b, cache.state, 0, step.cu_seqlens, step.state_slots, xbc)
+        ops.short_conv(proj, inner, conv_ch, self.conv, self.conv_b, cache.state, 0, step.cu_seqlens, step.state_slots, xbc,
+                       longest=step.max_query_len)
         y = ws.get(tag + "ssm.y", (T, inner), torch.float32)
         ops.ssd_scan(xbc, proj, width - s.num_heads, self.dt_bias, self.a_log, self.d, cache.state, (s.conv - 1) * conv_ch,
                      step.cu_seqlens, step.state_slots, y, s.num_heads, s.groups, s.state, s.vdim)
@@ -136,7 +138,8 @@ class DeltaRule:
 
     @staticmethod
     def cache_need(s: DeltaRuleSpec):
-        return FixedState(((s.conv - 1) * DeltaRule._conv_channels(s) + s.num_heads * s.dim * s.vdim,))
+        from ..csrc import ops
+        return FixedState(((s.conv - 1) * DeltaRule._conv_channels(s) + ops.scan_state_floats(s.num_heads, s.dim, s.vdim),))
 
     def __init__(self, s: DeltaRuleSpec, weights: dict, ctx):
         from ..csrc import ops
@@ -167,7 +170,8 @@ class DeltaRule:
         low = self.low_proj(h, step, "dr.low")
         up = self.up_proj(low, step, "dr.up")                      # [decay (H*D) | gate (H*P)]
         qkv = ws.get(tag + "dr.qkv", (T, C), torch.float32)
-        ops.short_conv(proj, 0, C, self.conv, None, cache.state, 0, step.cu_seqlens, step.state_slots, qkv)
+        ops.short_conv(proj, 0, C, self.conv, None, cache.state, 0, step.cu_seqlens, step.state_slots, qkv,
+                       longest=step.max_query_len)
         o = ws.get(tag + "dr.o", (T, H * P), torch.float32)
         ops.delta_scan(qkv, up, 0, self.dt_bias, self.a_log, proj, C, D ** -0.5, s.unit_eps, cache.state, (s.conv - 1) * C,
                        step.cu_seqlens, step.state_slots, o, H, G, D, P)
