@@ -1016,34 +1016,35 @@ def dyt_rows(x, delta, rows, alpha, weight, bias, out):
 
 
 # ---------------------------------------------------------------- recurrent mixers (csrc/recurrent.cu)
-RC_THREADS, RC_ROWS = 128, 16
+def scan_shape(n: int, columns: int):
+    """(rows a lane, lanes a column, threads a block, columns a block, blocks a head) of a scan over a state of n rows and
+    `columns` columns per head; the same arithmetic as csrc/recurrent.cu (scan_shape), on which the state's size rests."""
+    if not 0 < n <= 512 or columns <= 0:
+        raise KernelError(f"the scan kernels take states of 1 to 512 rows, got {n} x {columns}")
+    rows = 4 if n <= 128 else (8 if n <= 256 else 16)
+    L = 1
+    while L * rows < n:
+        L *= 2
+    threads = 128 if 128 // L >= columns else (256 if 256 // L >= columns else 512)
+    ct = threads // L
+    return rows, L, threads, ct, -(-columns // ct)
 
 
 def scan_lanes(n: int) -> int:
-    """Lanes that share one column of a state with n rows (what the scan kernels pick)."""
-    L = 1
-    while L * RC_ROWS < n:
-        L *= 2
-    if L > 32:
-        raise KernelError(f"the scan kernels take states of up to {32 * RC_ROWS} rows, got {n}")
-    return L
-
-
-def scan_column_tiles(n: int, columns: int) -> int:
-    ct = RC_THREADS // scan_lanes(n)
-    return -(-columns // ct)
+    return scan_shape(n, 1)[1]
 
 
 def scan_state_floats(H, n, P) -> int:
     """Floats of a recurrence's state (H heads of n x P numbers) in the layout the scan kernels keep it in: per head
     and tile of columns, the rows each lane holds, thread by thread."""
-    return H * scan_column_tiles(n, P) * RC_ROWS * RC_THREADS
+    rows, _, threads, _, Z = scan_shape(n, P)
+    return H * Z * rows * threads
 
 
 def mlstm_state_floats(H, D, P) -> int:
     """The matrix memory's state: S as `scan_state_floats`, then a normaliser [D] and a running maximum for every tile
     of columns of every head."""
-    Z = scan_column_tiles(D, P)
+    Z = scan_shape(D, P)[4]
     return scan_state_floats(H, D, P) + H * Z * D + H * Z
 
 

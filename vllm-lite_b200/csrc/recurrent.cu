@@ -19,27 +19,54 @@
 //                   before or after the norm
 //
 // Layout of the scans: a block owns (head, request, tile of value columns); a column of the state is held in
-// registers by L lanes of a warp (row r of the state by lane r mod L), so a token costs each lane N/L
-// multiply-adds and one or two butterfly sums over the L lanes.  The per-token vectors of a chunk of tokens
+// registers by L lanes of a warp (row r of the state by lane r mod L, four rows a lane where 32 lanes can hold
+// the column), so a token costs each lane a few multiply-adds and one or two butterfly sums over the L lanes,
+// and the sixteen warps of a block take turns on an SM while each waits for its sums.  The per-token vectors of a chunk of tokens
 // are staged in shared memory by the whole block, one chunk ahead of the walk.  The order of every sum depends
 // on the sizes alone, never on how the tokens were cut into steps or on what else the launch holds.
 #include "common.cuh"
 
-#define RC_THREADS 128
-#define RC_ROWS 16            // state rows per lane, at most
+#define RC_MAX_THREADS 512
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
-__device__ __forceinline__ float group_sum(float v, int L) {
+template <int L>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
     for (int o = L >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-static inline int lanes_for(int N) {
+// How a scan block is shaped for a state of N rows and P columns per head: a column is held by L lanes of a warp with
+// `rows` rows each (4 rows while 32 lanes can hold the column, so that many warps share the walk of a token; 8 or 16
+// for longer columns), and a block is 128, 256 or 512 threads: the fewest that hold all P columns, else 512.
+struct ScanShape { int rows, L, threads, CT, Z; };
+static inline bool scan_shape(int N, int P, ScanShape* sh) {
+    if (N <= 0 || P <= 0 || N > 512) return false;
+    sh->rows = N <= 128 ? 4 : (N <= 256 ? 8 : 16);
     int L = 1;
-    while (L * RC_ROWS < N) L <<= 1;
-    return L;
+    while (L * sh->rows < N) L <<= 1;
+    sh->L = L;
+    sh->threads = (128 / L >= P) ? 128 : ((256 / L >= P) ? 256 : RC_MAX_THREADS);
+    sh->CT = sh->threads / L;
+    sh->Z = (P + sh->CT - 1) / sh->CT;
+    return true;
 }
+// KERNEL<TP, rows, L> for the shape `sh`
+#define SCAN_LAUNCH(KERNEL, TP, sh, grid, smem, s, ...)                                                              \
+    do {                                                                                                             \
+        const dim3 block_(sh.threads);                                                                               \
+        if (sh.rows == 16) return vl_launch(KERNEL<TP, 16, 32>, grid, block_, smem, s, __VA_ARGS__);                 \
+        if (sh.rows == 8) return vl_launch(KERNEL<TP, 8, 32>, grid, block_, smem, s, __VA_ARGS__);                   \
+        switch (sh.L) {                                                                                              \
+            case 32: return vl_launch(KERNEL<TP, 4, 32>, grid, block_, smem, s, __VA_ARGS__);                        \
+            case 16: return vl_launch(KERNEL<TP, 4, 16>, grid, block_, smem, s, __VA_ARGS__);                        \
+            case 8: return vl_launch(KERNEL<TP, 4, 8>, grid, block_, smem, s, __VA_ARGS__);                          \
+            case 4: return vl_launch(KERNEL<TP, 4, 4>, grid, block_, smem, s, __VA_ARGS__);                          \
+            case 2: return vl_launch(KERNEL<TP, 4, 2>, grid, block_, smem, s, __VA_ARGS__);                          \
+            default: return vl_launch(KERNEL<TP, 4, 1>, grid, block_, smem, s, __VA_ARGS__);                         \
+        }                                                                                                            \
+    } while (0)
 
 // ------------------------------------------------------------------------------------------ convolution
 // A block owns 32 channels and CONV_TOKENS tokens of one request.  mode 0: outputs and the new state by the same block
@@ -114,13 +141,13 @@ extern "C" int vl_short_conv(const void* in, int dtype, int ld, int col0, int C,
 // afterwards, so the loads' latency hides behind the walk (RC_PREFETCH values per thread, which bounds the chunk).
 // A request's state lies in the order the block's threads hold it: [head][column tile][row i of a lane][thread], so
 // that loading and storing it are contiguous; the layout is the kernels' own business (vl_scan_state_floats).
-#define RC_PREFETCH 24
+#define RC_PREFETCH 8
 
 template <typename Raw>
 __device__ __forceinline__ void scan_prefetch(float (&pf)[RC_PREFETCH], int first_row, int m, int VEC, Raw raw) {
 #pragma unroll
     for (int j = 0; j < RC_PREFETCH; ++j) {
-        const int idx = threadIdx.x + j * RC_THREADS;
+        const int idx = threadIdx.x + j * blockDim.x;
         if (idx < m * VEC) {
             const int k = idx / VEC;
             pf[j] = raw(first_row + k, idx - k * VEC);
@@ -130,49 +157,49 @@ __device__ __forceinline__ void scan_prefetch(float (&pf)[RC_PREFETCH], int firs
 __device__ __forceinline__ void scan_commit(const float (&pf)[RC_PREFETCH], float* buf, int m, int VEC) {
 #pragma unroll
     for (int j = 0; j < RC_PREFETCH; ++j) {
-        const int idx = threadIdx.x + j * RC_THREADS;
+        const int idx = threadIdx.x + j * blockDim.x;
         if (idx < m * VEC) buf[idx] = pf[j];
     }
 }
-static inline int scan_chunk(int VEC) {
-    int m = RC_PREFETCH * RC_THREADS / VEC;
+static inline int scan_chunk(int VEC, int threads) {
+    int m = RC_PREFETCH * threads / VEC;
     return m < 1 ? 0 : (m > 16 ? 16 : m);
 }
+template <int ROWS>
 __device__ __forceinline__ float* scan_state(float* state, long long stride, int slot, int h) {
-    return state + (long long)slot * stride + ((size_t)h * gridDim.z + blockIdx.z) * RC_ROWS * RC_THREADS + threadIdx.x;
+    return state + (long long)slot * stride + ((size_t)h * gridDim.z + blockIdx.z) * ROWS * blockDim.x + threadIdx.x;
 }
 extern "C" long long vl_scan_state_floats(int H, int N, int P) {
-    const int L = lanes_for(N);
-    if (L > 32 || H <= 0 || N <= 0 || P <= 0) return -1;
-    const int CT = RC_THREADS / L, Z = (P + CT - 1) / CT;
-    return (long long)H * Z * RC_ROWS * RC_THREADS;
+    ScanShape sh;
+    if (H <= 0 || !scan_shape(N, P, &sh)) return -1;
+    return (long long)H * sh.Z * sh.rows * sh.threads;
 }
 
 // ------------------------------------------------------------------------------------------ state space
 // xbc float32 [T, C]: x (H*P) | B (G*N) | C (G*N), the convolution's output.  raw dt: column dt_col + h of `proj`.
 // y float32 [T, H*P].  Staged per token: B [N] | C [N] | x [CT] | dt | decay.
-template <typename TP>
-__global__ void __launch_bounds__(RC_THREADS)
+template <typename TP, int ROWS, int L>
+__global__ void __launch_bounds__(RC_MAX_THREADS)
 ssd_scan_kernel(const float* __restrict__ xbc, int C, const TP* __restrict__ proj, int ld, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dw,
                 float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                const int* __restrict__ slots, float* __restrict__ y, int H, int G, int N, int P, int L, int chunk) {
+                const int* __restrict__ slots, float* __restrict__ y, int H, int G, int N, int P, int chunk) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const int s0 = cu[b], n = cu[b + 1] - s0;
     if (n <= 0) return;
-    const int CT = RC_THREADS / L, tid = threadIdx.x;
+    const int NT = blockDim.x, CT = NT / L, tid = threadIdx.x;
     const int col = tid / L, l = tid % L;
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
     const int g = h / (H / G), inner = H * P;
     const int VEC = 2 * N + CT + 2;
-    float* S = scan_state(state, state_stride, slots[b], h);
-    float s[RC_ROWS];
+    float* S = scan_state<ROWS>(state, state_stride, slots[b], h);
+    float s[ROWS];
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) s[i] = S[(size_t)i * RC_THREADS];
+    for (int i = 0; i < ROWS; ++i) s[i] = S[(size_t)i * NT];
     const float rate = expf(A_log[h]), skip = Dw[h], bias = dt_bias[h];
     auto raw = [&](int row, int e) -> float {
         const float* src = xbc + (size_t)(s0 + row) * C;
@@ -205,14 +232,14 @@ ssd_scan_kernel(const float* __restrict__ xbc, int C, const TP* __restrict__ pro
             const float xv = v[2 * N + col], dx = v[2 * N + CT] * xv, a = v[2 * N + CT + 1];
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < RC_ROWS; ++i) {
+            for (int i = 0; i < ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < N) {
                     s[i] = a * s[i] + v[r] * dx;
                     acc += s[i] * v[N + r];
                 }
             }
-            acc = group_sum(acc, L);
+            acc = group_sum<L>(acc);
             if (live && l == 0) y[(size_t)(s0 + t0 + k) * inner + (size_t)h * P + p] = acc + skip * xv;
         }
         if (mn > 0) {
@@ -226,7 +253,7 @@ ssd_scan_kernel(const float* __restrict__ xbc, int C, const TP* __restrict__ pro
         m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) S[(size_t)i * RC_THREADS] = s[i];
+    for (int i = 0; i < ROWS; ++i) S[(size_t)i * NT] = s[i];
 }
 
 extern "C" int vl_ssd_scan(const float* xbc, int C, const void* proj, int dtype, int ld, int dt_col, const float* dt_bias,
@@ -234,19 +261,19 @@ extern "C" int vl_ssd_scan(const float* xbc, int C, const void* proj, int dtype,
                            const int* slots, int B, float* y, int H, int G, int N, int P, void* stream) {
     if (B <= 0) return VL_OK;
     if (H <= 0 || G <= 0 || H % G || N <= 0 || P <= 0 || C != H * P + 2 * G * N) return VL_ERR_ARGUMENT;
-    const int L = lanes_for(N);
-    if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L, VEC = 2 * N + CT + 2, chunk = scan_chunk(VEC);
+    ScanShape sh;
+    if (!scan_shape(N, P, &sh)) return VL_ERR_UNSUPPORTED;
+    const int CT = sh.CT, VEC = 2 * N + CT + 2, chunk = scan_chunk(VEC, sh.threads);
     if (!chunk) return VL_ERR_UNSUPPORTED;
-    dim3 grid(H, B, (P + CT - 1) / CT);
+    dim3 grid(H, B, sh.Z);
     const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        return vl_launch(ssd_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, xbc, C, (const float*)proj, ld, dt_col,
-                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L, chunk);
+        SCAN_LAUNCH(ssd_scan_kernel, float, sh, grid, smem, s, xbc, C, (const float*)proj, ld, dt_col,
+                    dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, chunk);
     if (dtype == VL_BF16)
-        return vl_launch(ssd_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, xbc, C, (const bf16*)proj, ld, dt_col,
-                         dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, L, chunk);
+        SCAN_LAUNCH(ssd_scan_kernel, bf16, sh, grid, smem, s, xbc, C, (const bf16*)proj, ld, dt_col,
+                    dt_bias, A_log, Dw, state, state_stride, cu, slots, y, H, G, N, P, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 
@@ -255,12 +282,12 @@ extern "C" int vl_ssd_scan(const float* xbc, int C, const void* proj, int dtype,
 // state per slot: S in the scans' layout, then n [H][Z][D], then m [H][Z], Z = the number of column tiles of a head
 // (vl_mlstm_state_floats): blocks of one head run at different times, so each keeps its own n and m.  o float32 [T, H*P].
 // Staged per token: q [D] (scaled) | k [D] | v [CT] | keep | put | floor  (the raw gates arrive in the first two of these).
-template <typename TP>
-__global__ void __launch_bounds__(RC_THREADS)
+template <typename TP, int ROWS, int L>
+__global__ void __launch_bounds__(RC_MAX_THREADS)
 mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale, float den_eps,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int L, int chunk) {
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int chunk) {
     extern __shared__ float sm[];
     __shared__ float sM;
     pdl_launch_dependents();
@@ -268,21 +295,21 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
     const int h = blockIdx.x, b = blockIdx.y;
     const int s0 = cu[b], n = cu[b + 1] - s0;
     if (n <= 0) return;
-    const int CT = RC_THREADS / L, tid = threadIdx.x;
+    const int NT = blockDim.x, CT = NT / L, tid = threadIdx.x;
     const int col = tid / L, l = tid % L;
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
     const int VEC = 2 * D + CT + 3;
     const int Z = gridDim.z, z = blockIdx.z;
-    float* S = scan_state(state, state_stride, slots[b], h);
-    float* base = state + (long long)slots[b] * state_stride + (size_t)H * Z * RC_ROWS * RC_THREADS;
+    float* S = scan_state<ROWS>(state, state_stride, slots[b], h);
+    float* base = state + (long long)slots[b] * state_stride + (size_t)H * Z * ROWS * NT;
     float* nv = base + ((size_t)h * Z + z) * D;
     float* mv = base + (size_t)H * Z * D + (size_t)h * Z + z;
-    float s[RC_ROWS], nr[RC_ROWS];
+    float s[ROWS], nr[ROWS];
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
+    for (int i = 0; i < ROWS; ++i) {
         const int r = l + L * i;
-        s[i] = S[(size_t)i * RC_THREADS];
+        s[i] = S[(size_t)i * NT];
         nr[i] = r < D ? nv[r] : 0.f;
     }
     if (tid == 0) sM = mv[0];
@@ -295,21 +322,31 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
         if (e == 2 * D + CT) return to_f32(src[i_col + h]);
         return e == 2 * D + CT + 1 ? to_f32(src[f_col + h]) : 0.f;
     };
-    auto finish = [&](float* buf, int m) {                            // the gates and the running maximum, token after token
+    auto finish = [&](float* buf, int m) {       // the gates (every token by itself), the running maximum (a chain), the exponentials
+        if (tid < m) {
+            float* v = buf + (size_t)tid * VEC + 2 * D + CT;
+            const float fa = cap * tanhf((v[1] + fb) / cap);
+            v[0] = cap * tanhf((v[0] + ib) / cap);
+            v[1] = fminf(fa, 0.f) - log1pf(expf(-fabsf(fa)));                        // log sigmoid
+        }
+        __syncthreads();
         if (tid == 0) {
             float mx = sM;
             for (int k = 0; k < m; ++k) {
                 float* v = buf + (size_t)k * VEC + 2 * D + CT;
-                const float ig = cap * tanhf((v[0] + ib) / cap);
-                const float fa = cap * tanhf((v[1] + fb) / cap);
-                const float fg = fminf(fa, 0.f) - log1pf(expf(-fabsf(fa)));          // log sigmoid
+                const float ig = v[0], fg = v[1];
                 const float nm = fmaxf(fg + mx, ig);
-                v[0] = expf(fg + mx - nm);
-                v[1] = expf(ig - nm);
-                v[2] = expf(-nm);
+                v[0] = fg + mx - nm;
+                v[1] = ig - nm;
+                v[2] = -nm;
                 mx = nm;
             }
             sM = mx;
+        }
+        __syncthreads();
+        if (tid < 3 * m) {
+            float* v = buf + (size_t)(tid / 3) * VEC + 2 * D + CT + tid % 3;
+            v[0] = expf(v[0]);
         }
     };
     float pf[RC_PREFETCH];
@@ -329,7 +366,7 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
             const float keep = v[2 * D + CT], put = v[2 * D + CT + 1], pv = put * v[2 * D + col];
             float acc = 0.f, den = 0.f;
 #pragma unroll
-            for (int i = 0; i < RC_ROWS; ++i) {
+            for (int i = 0; i < ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
                     const float kv = v[D + r], qv = v[r];
@@ -339,8 +376,8 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
                     den += nr[i] * qv;
                 }
             }
-            acc = group_sum(acc, L);
-            den = group_sum(den, L);
+            acc = group_sum<L>(acc);
+            den = group_sum<L>(den);
             if (live && l == 0)
                 o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc / (fmaxf(fabsf(den), v[2 * D + CT + 2]) + den_eps);
         }
@@ -355,19 +392,18 @@ mlstm_scan_kernel(const TP* __restrict__ proj, int ld, int q_col, int k_col, int
         m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) {
+    for (int i = 0; i < ROWS; ++i) {
         const int r = l + L * i;
-        S[(size_t)i * RC_THREADS] = s[i];
+        S[(size_t)i * NT] = s[i];
         if (col == 0 && r < D) nv[r] = nr[i];
     }
     if (tid == 0) mv[0] = sM;
 }
 
 extern "C" long long vl_mlstm_state_floats(int H, int D, int P) {
-    const int L = lanes_for(D);
-    if (L > 32 || H <= 0 || D <= 0 || P <= 0) return -1;
-    const int CT = RC_THREADS / L, Z = (P + CT - 1) / CT;
-    return (long long)H * Z * RC_ROWS * RC_THREADS + (long long)H * Z * D + (long long)H * Z;
+    ScanShape sh;
+    if (H <= 0 || !scan_shape(D, P, &sh)) return -1;
+    return (long long)H * sh.Z * sh.rows * sh.threads + (long long)H * sh.Z * D + (long long)H * sh.Z;
 }
 
 extern "C" int vl_mlstm_scan(const void* proj, int dtype, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
@@ -376,19 +412,19 @@ extern "C" int vl_mlstm_scan(const void* proj, int dtype, int ld, int q_col, int
                              void* stream) {
     if (B <= 0) return VL_OK;
     if (H <= 0 || D <= 0 || P <= 0 || !(cap > 0.f)) return VL_ERR_ARGUMENT;
-    const int L = lanes_for(D);
-    if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L, VEC = 2 * D + CT + 3, chunk = scan_chunk(VEC);
+    ScanShape sh;
+    if (!scan_shape(D, P, &sh)) return VL_ERR_UNSUPPORTED;
+    const int CT = sh.CT, VEC = 2 * D + CT + 3, chunk = scan_chunk(VEC, sh.threads);
     if (!chunk) return VL_ERR_UNSUPPORTED;
-    dim3 grid(H, B, (P + CT - 1) / CT);
+    dim3 grid(H, B, sh.Z);
     const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        return vl_launch(mlstm_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, (const float*)proj, ld, q_col, k_col, v_col,
-                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L, chunk);
+        SCAN_LAUNCH(mlstm_scan_kernel, float, sh, grid, smem, s, (const float*)proj, ld, q_col, k_col, v_col,
+                    i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, chunk);
     if (dtype == VL_BF16)
-        return vl_launch(mlstm_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, (const bf16*)proj, ld, q_col, k_col, v_col,
-                         i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, L, chunk);
+        SCAN_LAUNCH(mlstm_scan_kernel, bf16, sh, grid, smem, s, (const bf16*)proj, ld, q_col, k_col, v_col,
+                    i_col, f_col, i_bias, f_bias, cap, q_scale, den_eps, state, state_stride, cu, slots, o, H, D, P, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 
@@ -397,29 +433,29 @@ extern "C" int vl_mlstm_scan(const void* proj, int dtype, int ld, int q_col, int
 // raw beta: column beta_col + h of `proj`.  o float32 [T, H*P].
 // Staged per token: q [D] | k [D] | decay [D] | v [CT] | beta; a warp per token then makes q and k unit vectors (q scaled),
 // the decays exp(-rate softplus(raw + bias)) and beta a sigmoid.
-template <typename TP>
-__global__ void __launch_bounds__(RC_THREADS)
+template <typename TP, int ROWS, int L>
+__global__ void __launch_bounds__(RC_MAX_THREADS)
 delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ decay, int dld, int dcol,
                   const float* __restrict__ dt_bias,
                   const float* __restrict__ A_log, const TP* __restrict__ proj, int ld, int beta_col, float q_scale,
                   float unit_eps, float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int G, int D, int P, int L, int chunk) {
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int G, int D, int P, int chunk) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const int s0 = cu[b], n = cu[b + 1] - s0;
     if (n <= 0) return;
-    const int CT = RC_THREADS / L, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NT = blockDim.x, CT = NT / L, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int col = tid / L, l = tid % L;
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
     const int g = h / (H / G);
     const int VEC = 3 * D + CT + 1;
-    float* S = scan_state(state, state_stride, slots[b], h);
-    float s[RC_ROWS];
+    float* S = scan_state<ROWS>(state, state_stride, slots[b], h);
+    float s[ROWS];
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) s[i] = S[(size_t)i * RC_THREADS];
+    for (int i = 0; i < ROWS; ++i) s[i] = S[(size_t)i * NT];
     const float rate = expf(A_log[h]);
     auto raw = [&](int row, int e) -> float {
         const size_t t = (size_t)(s0 + row);
@@ -429,7 +465,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ d
         return to_f32(proj[t * ld + beta_col + h]);
     };
     auto finish = [&](float* buf, int m) {
-        for (int k = warp; k < m; k += RC_THREADS / 32) {
+        for (int k = warp; k < m; k += NT / 32) {
             float* v = buf + (size_t)k * VEC;
             float qq = 0.f, kk = 0.f;
             for (int r = lane; r < D; r += 32) { qq += v[r] * v[r]; kk += v[D + r] * v[D + r]; }
@@ -460,25 +496,25 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ d
             const float* v = buf + (size_t)k * VEC;
             float back = 0.f;
 #pragma unroll
-            for (int i = 0; i < RC_ROWS; ++i) {
+            for (int i = 0; i < ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
                     s[i] *= v[2 * D + r];
                     back += s[i] * v[D + r];
                 }
             }
-            back = group_sum(back, L);
+            back = group_sum<L>(back);
             const float u = v[3 * D + CT] * (v[3 * D + col] - back);
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < RC_ROWS; ++i) {
+            for (int i = 0; i < ROWS; ++i) {
                 const int r = l + L * i;
                 if (r < D) {
                     s[i] += v[D + r] * u;
                     acc += s[i] * v[r];
                 }
             }
-            acc = group_sum(acc, L);
+            acc = group_sum<L>(acc);
             if (live && l == 0) o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc;
         }
         if (mn > 0) {
@@ -492,7 +528,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const TP* __restrict__ d
         m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < RC_ROWS; ++i) S[(size_t)i * RC_THREADS] = s[i];
+    for (int i = 0; i < ROWS; ++i) S[(size_t)i * NT] = s[i];
 }
 
 extern "C" int vl_delta_scan(const float* qkv, int C, const void* decay, int dld, int dcol, const float* dt_bias, const float* A_log,
@@ -501,19 +537,19 @@ extern "C" int vl_delta_scan(const float* qkv, int C, const void* decay, int dld
                              int P, void* stream) {
     if (B <= 0) return VL_OK;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || P <= 0 || C != 2 * G * D + H * P) return VL_ERR_ARGUMENT;
-    const int L = lanes_for(D);
-    if (L > 32) return VL_ERR_UNSUPPORTED;
-    const int CT = RC_THREADS / L, VEC = 3 * D + CT + 1, chunk = scan_chunk(VEC);
+    ScanShape sh;
+    if (!scan_shape(D, P, &sh)) return VL_ERR_UNSUPPORTED;
+    const int CT = sh.CT, VEC = 3 * D + CT + 1, chunk = scan_chunk(VEC, sh.threads);
     if (!chunk) return VL_ERR_UNSUPPORTED;
-    dim3 grid(H, B, (P + CT - 1) / CT);
+    dim3 grid(H, B, sh.Z);
     const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        return vl_launch(delta_scan_kernel<float>, grid, dim3(RC_THREADS), smem, s, qkv, C, (const float*)decay, dld, dcol, dt_bias, A_log,
-                         (const float*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L, chunk);
+        SCAN_LAUNCH(delta_scan_kernel, float, sh, grid, smem, s, qkv, C, (const float*)decay, dld, dcol, dt_bias, A_log,
+                    (const float*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, chunk);
     if (dtype == VL_BF16)
-        return vl_launch(delta_scan_kernel<bf16>, grid, dim3(RC_THREADS), smem, s, qkv, C, (const bf16*)decay, dld, dcol, dt_bias, A_log,
-                         (const bf16*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, L, chunk);
+        SCAN_LAUNCH(delta_scan_kernel, bf16, sh, grid, smem, s, qkv, C, (const bf16*)decay, dld, dcol, dt_bias, A_log,
+                    (const bf16*)proj, ld, beta_col, q_scale, unit_eps, state, state_stride, cu, slots, o, H, G, D, P, chunk);
     return VL_ERR_UNSUPPORTED;
 }
 
