@@ -559,7 +559,26 @@ extern "C" int vl_delta_scan(const float* qkv, int C, const void* decay, int dld
 // w float32 [wlen], indexed by column modulo wlen (wlen = W: one weight per column; wlen = part: shared by the parts).
 #define RC_GATE_SILU 1
 #define RC_GATE_SIGMOID 2
-template <typename TP>
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b));
+}
+
+// VEC = 4: a lane takes four neighbouring columns at a time (16-byte reads of y, 8- or 16-byte accesses of gate and out);
+// the launcher picks it when every row and part starts on such a boundary.
+template <typename TP, int VEC>
 __global__ void __launch_bounds__(128)
 gate_norm_kernel(const float* __restrict__ y, const TP* __restrict__ gate, int ld, int gate_col, int gate_kind, int gate_first,
                  const float* __restrict__ w, int wlen, float eps, TP* __restrict__ out, int W, int part, size_t groups) {
@@ -574,26 +593,36 @@ gate_norm_kernel(const float* __restrict__ y, const TP* __restrict__ gate, int l
     const float* row = y + t * W + c0;
     const TP* grow = gate ? gate + t * ld + gate_col + c0 : nullptr;
     float ss = 0.f;
-    for (int c = lane; c < part; c += 32) {
-        float v = row[c];
+    for (int c = lane * VEC; c < part; c += 32 * VEC) {
+        float v[VEC], g[VEC];
+        if (VEC == 4) load4(row + c, reinterpret_cast<float (&)[4]>(v)); else v[0] = row[c];
         if (gate_first && grow) {
-            const float gv = to_f32(grow[c]);
-            v *= gate_kind == RC_GATE_SILU ? silu_f(gv) : sigmoid_f(gv);
+            if (VEC == 4) load4(grow + c, reinterpret_cast<float (&)[4]>(g)); else g[0] = to_f32(grow[c]);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] *= gate_kind == RC_GATE_SILU ? silu_f(g[e]) : sigmoid_f(g[e]);
         }
-        ss += v * v;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss += v[e] * v[e];
     }
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / part + eps);
-    for (int c = lane; c < part; c += 32) {
-        float v = row[c];
-        float gv = 1.f;
+    for (int c = lane * VEC; c < part; c += 32 * VEC) {
+        float v[VEC], g[VEC];
+        if (VEC == 4) load4(row + c, reinterpret_cast<float (&)[4]>(v)); else v[0] = row[c];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) g[e] = 1.f;
         if (grow) {
-            gv = to_f32(grow[c]);
-            gv = gate_kind == RC_GATE_SILU ? silu_f(gv) : sigmoid_f(gv);
+            if (VEC == 4) load4(grow + c, reinterpret_cast<float (&)[4]>(g)); else g[0] = to_f32(grow[c]);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) g[e] = gate_kind == RC_GATE_SILU ? silu_f(g[e]) : sigmoid_f(g[e]);
         }
-        if (gate_first) v = v * gv * inv * w[(c0 + c) % wlen];
-        else v = v * inv * w[(c0 + c) % wlen] * gv;
-        out[t * W + c0 + c] = from_f32<TP>(v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const float wv = w[(c0 + c + e) % wlen];
+            v[e] = gate_first ? v[e] * g[e] * inv * wv : v[e] * inv * wv * g[e];
+        }
+        if (VEC == 4) store4(out + t * W + c0 + c, reinterpret_cast<const float (&)[4]>(v));
+        else out[t * W + c0 + c] = from_f32<TP>(v[0]);
     }
 }
 
@@ -604,11 +633,19 @@ extern "C" int vl_gate_norm(const float* y, const void* gate, int dtype, int ld,
     const size_t groups = (size_t)T * (W / part);
     const unsigned blocks = (unsigned)((groups + 3) / 4);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return vl_launch(gate_norm_kernel<float>, dim3(blocks), dim3(128), 0, s, y, (const float*)gate, ld, gate_col, gate_kind,
+    const bool vec = part % 4 == 0 && W % 4 == 0 && ld % 4 == 0 && gate_col % 4 == 0 &&
+                     (((uintptr_t)y | (uintptr_t)gate | (uintptr_t)out) & 15) == 0;
+    if (dtype == VL_F32) {
+        if (vec) return vl_launch(gate_norm_kernel<float, 4>, dim3(blocks), dim3(128), 0, s, y, (const float*)gate, ld, gate_col,
+                                  gate_kind, gate_first, w, wlen, eps, (float*)out, W, part, groups);
+        return vl_launch(gate_norm_kernel<float, 1>, dim3(blocks), dim3(128), 0, s, y, (const float*)gate, ld, gate_col, gate_kind,
                          gate_first, w, wlen, eps, (float*)out, W, part, groups);
-    if (dtype == VL_BF16)
-        return vl_launch(gate_norm_kernel<bf16>, dim3(blocks), dim3(128), 0, s, y, (const bf16*)gate, ld, gate_col, gate_kind,
+    }
+    if (dtype == VL_BF16) {
+        if (vec) return vl_launch(gate_norm_kernel<bf16, 4>, dim3(blocks), dim3(128), 0, s, y, (const bf16*)gate, ld, gate_col,
+                                  gate_kind, gate_first, w, wlen, eps, (bf16*)out, W, part, groups);
+        return vl_launch(gate_norm_kernel<bf16, 1>, dim3(blocks), dim3(128), 0, s, y, (const bf16*)gate, ld, gate_col, gate_kind,
                          gate_first, w, wlen, eps, (bf16*)out, W, part, groups);
+    }
     return VL_ERR_UNSUPPORTED;
 }
