@@ -586,8 +586,8 @@ TUZISUN_SIZES = {"2k": (2048, 4, 16, 4, 128, 1024, 32, 64, 128, 4, 8, 128, 256, 
 
 def tuzisun_config(size, layers):
     (W, S, H, KV, D, win, SH, SP, N, taps, MH, MD, MP, DH, DD, DP, rank, ff, eff, E, top, groups, keep, vocab) = TUZISUN_SIZES[size]
-    par = dict(left=dict(heads=H, kv_heads=KV, dim=D, vdim=D, scale=D ** -0.5, mask=dict(size=win), rot=dict(dims=D, base=250000.0)),
-               right=dict(heads=SH, vdim=SP, state=N, groups=1, conv=taps, norm_groups=8), left_scale=0.8, right_scale=0.9)
+    par = dict(left=dict(heads=H, kv_heads=KV, dim=D, vdim=D, scale=D ** -0.5, mask=dict(size=win), rot=dict(dims=D, base=500000.0)),
+               right=dict(heads=SH, vdim=SP, state=N, groups=1, conv=taps, norm_groups=8), left_scale=0.7, right_scale=1.1)
     moe = dict(kind="moe", expert=dict(ff=eff), router=dict(experts=E, top=top, groups=dict(count=groups, keep=keep)))
     dense = dict(kind="dense", ff=ff, limit=7.0)
     kinds = [("channel_delta", dict(heads=DH, kv_heads=DH, dim=DD, vdim=DP, conv=taps, decay_rank=rank, gate_rank=rank), dense),

@@ -69,9 +69,9 @@ CONFIGS = {
                       layer("channel_delta", delta(2, 2, 40, 8, 2, 5, 7), dense(40, 1.5)),
                       layer("parallel", parallel(2, 1, 48, 48, 100, 16, 777.0, 0.3, 2, 24, 8, 2, 4, 2, 0.5, 0.5), moe(24, 8, 3, 2, 1))]),
     "C": dict(architecture="Tuzisun", vocab=301, width=128, streams=4, norm=dict(eps=1e-6),
-              layers=[layer("parallel", parallel(8, 1, 64, 64, 70, 64, 250000.0, 0.25, 4, 32, 128, 2, 5, 4, 0.8, 0.9), dense(160, 1.0)),
+              layers=[layer("parallel", parallel(8, 1, 64, 64, 70, 64, 300000.0, 0.25, 4, 32, 128, 2, 5, 4, 0.75, 0.95), dense(160, 1.0)),
                       layer("channel_delta", delta(4, 1, 128, 32, 3, 16, 16), moe(64, 8, 2, 4, 2)),
-                      layer("mlstm", mlstm(4, 64, 96, 12.0), dense(136, 1.0))]),
+                      layer("mlstm", mlstm(4, 64, 96, 10.0), dense(136, 1.25))]),
 }
 # D: sizes that are multiples of two at best: key heads of 20 and value heads of 12 numbers (padded to 32 for the kernels),
 #    three rotated pairs, a state of 10 rows, ONE tap (a convolution without memory), every expert chosen, two streams.
@@ -162,13 +162,13 @@ def make_runner(which, dtype, num_pages, sharp=1.0, page_size=None, max_requests
                        page_size=page_size or PAGE[which], num_pages=num_pages, max_requests=max_requests, max_context=1024, **kw)
 
 
-def assert_rows(rows, which, requests, dtype, what, sharp=1.0):
+def assert_rows(rows, which, requests, dtype, what, sharp=1.0, loosen=1.0):
     assert rows, "nothing was compared"
     bad, worst = [], 0.0
     for (rid, pos), row in rows.items():
         ref = plain_run(which, requests[rid], dtype, sharp)[0][pos]
         err = float((row - ref).abs().max()) / max(float(ref.abs().max()), 1e-12)
-        if err > tol(which, dtype):
+        if err > loosen * tol(which, dtype):
             bad.append((rid, pos, err))
         else:
             worst = max(worst, err)
@@ -616,7 +616,9 @@ def test_window_edges_show_in_the_logits(which):
         assert gap > 100 * tol(which, "float32"), f"a window off by {off} would not show ({gap:.2e})"
     runner = make_runner(which, "float32", num_pages=pages_for(which, 150) + 1, sharp=sharp)
     schedule = [([("r", toks[:60], list(range(60)))], [])] + [([("r", [toks[p]], [0])], []) for p in range(60, 150)]
-    assert_rows(H.run_schedule(runner, schedule), which, {"r": toks}, "float32", "window edges", sharp)
+    # scores forty times as large carry forty times the rounding of q.k into the exponentials: three times the tolerance,
+    # which the gap shown above still exceeds thirty times over
+    assert_rows(H.run_schedule(runner, schedule), which, {"r": toks}, "float32", "window edges", sharp, loosen=3.0)
 
 
 @pytest.mark.gpu
