@@ -622,6 +622,40 @@ def test_window_edges_show_in_the_logits(which):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_long_prompt_whole_against_portions(which):
+    """A prompt of 2,300 tokens in one step (the products, the experts and the attention of many rows run on their
+    tensor-core kernels for long steps, the convolution is cut among blocks, the scans walk thousands of tokens) against
+    the same prompt in portions of a few hundred tokens (the kernels of short steps): bfloat16 both, so they agree to rounding;
+    float32 bit for bit."""
+    from vllm_lite_b200.engine import ModelRunner, load_model_dir
+    n = 2300
+    toks = tokens_for(which, n, 71)
+    want = sorted(set(range(0, n, 97)) | set(range(n - 8, n)))
+    for dtype in ("bfloat16", "float32"):
+        _, plan, weights = load_model_dir(model_dir(which, store_of(dtype)), dtype, DEV)
+        runner = ModelRunner(plan, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device=DEV,
+                             page_size=PAGE[which], num_pages=pages_for(which, n) + 2, max_requests=2, max_context=4096)
+        whole = H.run_schedule(runner, [([("w", toks, want)], ["w"])])
+        cuts, schedule, at = [300, 411, 2, 600, 87, 900], [], 0
+        for c in cuts:
+            schedule.append(([("p", toks[at:at + c], [p - at for p in want if at <= p < at + c])], []))
+            at += c
+        assert at == n
+        parts = H.run_schedule(runner, schedule)
+        errs = []
+        for p in want:
+            a, b = whole[("w", p)], parts[("p", p)]
+            if dtype == "float32":
+                assert torch.equal(a, b), f"{which}: position {p} depends on the cut"
+            errs.append(float((a - b).abs().max()) / max(float(b.abs().max()), 1e-12))
+        if dtype == "bfloat16":
+            errs.sort()
+            assert errs[len(errs) // 2] <= tol(which, dtype) and errs[int(0.8 * len(errs))] <= 2 * tol(which, dtype), errs[-5:]
+        del runner
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(dtype):
     which, length = "B", 420
