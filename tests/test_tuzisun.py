@@ -349,6 +349,10 @@ RECURRENT = [
     ("matrix_memory", dict(num_heads=3, dim=72, vdim=136, gate_cap=15.0)),
     ("delta_rule", dict(num_heads=4, num_kv_heads=2, dim=16, vdim=24, conv=4, decay_rank=8, gate_rank=12)),
     ("delta_rule", dict(num_heads=2, num_kv_heads=1, dim=136, vdim=8, conv=2, decay_rank=5, gate_rank=7)),
+    # columns of more than 256 rows: sixteen rows a lane; of 512: the most the kernels take
+    ("state_space", dict(num_heads=2, vdim=12, state=264, groups=2, conv=2, norm_groups=2)),
+    ("matrix_memory", dict(num_heads=1, dim=300, vdim=20, gate_cap=10.0)),
+    ("delta_rule", dict(num_heads=2, num_kv_heads=2, dim=512, vdim=24, conv=3, decay_rank=4, gate_rank=4)),
 ]
 
 
