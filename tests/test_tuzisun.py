@@ -691,6 +691,27 @@ def test_greedy_generation_through_the_engine(which):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("which", ["C", "E"])
+def test_greedy_generation_bfloat16_with_the_cache_sized_from_memory(which):
+    """kv_blocks=None: pools (none at all for a model without attention) and state slots are sized from the GPU's free
+    memory; the tokens the bfloat16 engine picks lie at or near the plain implementation's maximum."""
+    from vllm_lite_b200 import LLMEngine
+    prompts = [tokens_for(which, n, 80 + i) for i, n in enumerate([9, 70])]
+    eng = LLMEngine(str(model_dir(which, "bfloat16")), dtype="bfloat16", kv_blocks=None, block_size=PAGE[which], max_batch_size=4,
+                    max_model_len=256)
+    outs = eng.generate(prompts, max_tokens=10)
+    far = 0
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        assert len(o) == 10
+        for t in o:
+            row = plain_run(which, toks, "bfloat16")[0][-1]
+            far += float(row.max() - row[t]) > 2 * tol(which, "bfloat16") * float(row.abs().max())
+            toks.append(t)
+    assert far <= 2
+
+
+@pytest.mark.gpu
 def test_command_line_and_replay_program(tmp_path):
     """The command line writes a folder from config.json and generates from it (greedy, float32: the plain implementation's
     tokens); bin/trace_run replays steps on the folder after the two low ranks were taken out of its config.json (the

@@ -33,29 +33,51 @@ def state_bytes(layout: CacheLayout, max_requests: int) -> int:
     return total
 
 
+def _mixer_width(mixer) -> int:
+    """Elements per token of a mixer's intermediates (float32 buffers count twice), a bound for the reserve."""
+    if mixer is None:
+        return 0
+    if hasattr(mixer, "left") and hasattr(mixer, "right"):              # two mixers side by side, plus their sum
+        return _mixer_width(mixer.left) + _mixer_width(mixer.right) + 2 * getattr(mixer.left, "hidden_size", 0)
+    if hasattr(mixer, "num_kv_heads") and hasattr(mixer, "head_dim"):
+        hd = max(mixer.head_dim, getattr(mixer, "v_head_dim", None) or 0)
+        return (2 * mixer.num_heads + 2 * mixer.num_kv_heads) * (-(-hd // 16) * 16)
+    if hasattr(mixer, "kv_rank"):
+        # latent attention: both latents, the queries, their absorbed form and the context (heads x cached row, the
+        # row rounded up to 16), the expanded values
+        row = -(-mixer.kv_rank // 16) * 16
+        return mixer.q_rank + mixer.kv_rank + mixer.num_heads * (mixer.dim + 2 * row + mixer.vdim)
+    if hasattr(mixer, "state") and hasattr(mixer, "norm_groups"):       # state space: projection, convolved copy, scan, gated
+        inner = mixer.num_heads * mixer.vdim
+        conv = inner + 2 * mixer.groups * mixer.state
+        return (inner + conv + mixer.num_heads) + 2 * conv + 2 * inner + inner
+    if hasattr(mixer, "gate_cap"):                                      # matrix memory
+        hp, hd = mixer.num_heads * mixer.vdim, mixer.num_heads * mixer.dim
+        return (2 * hd + 2 * hp + 2 * mixer.num_heads) + 2 * hp + hp
+    if hasattr(mixer, "decay_rank"):                                    # delta rule
+        hp, hd = mixer.num_heads * mixer.vdim, mixer.num_heads * mixer.dim
+        conv = 2 * mixer.num_kv_heads * mixer.dim + hp
+        return (conv + mixer.num_heads) + (mixer.decay_rank + mixer.gate_rank) + (hd + hp) + 2 * conv + 2 * hp + hp
+    return 0
+
+
 def activation_reserve(plan, max_step_tokens: int, max_requests: int, max_context: int, itemsize: int) -> int:
     """A bound on what steps allocate beside weights and cache: the buffers of the longest step (the
     float32 stream, a layer's widest intermediates) and, for every decode graph that may be recorded
     (batch buckets up to max_requests, context bounds from 1,024 up), its own logits."""
     H, V = plan.hidden_size, plan.vocab_size
-    widest = 0
+    widest, streams = 0, 1
     for block in plan.layers:
-        w = 0
         mixer, ffn = getattr(block, "mixer", None), getattr(block, "ffn", None)
-        if hasattr(mixer, "num_kv_heads"):
-            w += (2 * mixer.num_heads + 2 * mixer.num_kv_heads) * mixer.head_dim
-        elif hasattr(mixer, "kv_rank"):
-            # latent attention: both latents, the queries, their absorbed form and the context (heads x cached row, the
-            # row rounded up to 16), the expanded values
-            row = -(-mixer.kv_rank // 16) * 16
-            w += mixer.q_rank + mixer.kv_rank + mixer.num_heads * (mixer.dim + 2 * row + mixer.vdim)
+        streams = max(streams, int(getattr(block, "streams", 1) or 1))
+        w = _mixer_width(mixer)
         if hasattr(ffn, "top"):
             # routed experts: every token's row `top` times (sorted copy, gate and up, activation, result), tiles padded
             w += 2 * ffn.top * (3 * ffn.intermediate_size + 2 * H)
         elif hasattr(ffn, "intermediate_size"):
             w += 3 * ffn.intermediate_size
         widest = max(widest, w)
-    per_token = 4 * H + itemsize * (widest + 4 * H)
+    per_token = 4 * H * (1 + (streams if streams > 1 else 0)) + itemsize * (widest + 4 * H)
     bounds, b = 1, 1024
     while b < max_context:
         b, bounds = b * 2, bounds + 1

@@ -1078,6 +1078,9 @@ def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=T
     _check(_fn("recurrent", "vl_short_conv")(_ptr(x), dtype_code(x.dtype), x.shape[1], col0, C, _ptr(weight), _ptr(bias), taps,
                                              sp, stride, _ptr(cu), _ptr(slots), B, int(longest or max(x.shape[0], 1)), _ptr(out),
                                              int(bool(act)), _stream()), "vl_short_conv")
+    if int(longest or x.shape[0]) > 64:
+        global launch_count
+        launch_count += 1           # requests cut among blocks: the new state is a launch of its own
     return out
 
 
